@@ -2,9 +2,9 @@
 of the schedule that keeps any, and per-sequence state of fixed size.
 
 Runs with the same need (kv heads, head size, window) form a *group* with storage of
-its own: one pool ``[runs, 2, blocks, kv_heads * block_tokens * head_dim]`` (keys at index
-0 laid out ``[kv_heads, block_tokens, head_dim]`` inside a block, values at 1 laid out
-transposed, ``[kv_heads, head_dim, block_tokens]``) and one block table, so that, say, windowed layers give blocks back
+its own: per run one piece of memory that holds the key pool (``[blocks, kv_heads, block_tokens, head_dim]``)
+followed by the value pool (transposed inside a block, ``[blocks, kv_heads, value_dim, block_tokens]``; a value
+head may have another size than a key head), and one block table, so that, say, windowed layers give blocks back
 while full-attention layers keep theirs.  State needs are grouped the same way into
 ``[runs, slots, *shape]`` tensors, zeroed when a slot is handed out.
 
@@ -30,7 +30,7 @@ class KVGroup:
     need: KVNeed
     runs: list[int]                 # schedule entries that own a cache in this group
     table: BlockTable
-    storage: torch.Tensor | None    # [runs, 2, blocks, kv_heads * BLOCK_TOKENS * head_dim]
+    storage: torch.Tensor | None    # [runs, blocks * kv_heads * BLOCK_TOKENS * (head_dim + value_dim)]: keys, then values
 
     def bytes(self) -> int:
         return 0 if self.storage is None else self.storage.numel() * self.storage.element_size()
@@ -49,7 +49,7 @@ class RunCache:
 
     group: int | None               # index of its KV group, None if it keeps no keys
     k_pool: torch.Tensor | None     # [blocks, kv_heads, BLOCK_TOKENS, head_dim]
-    v_pool: torch.Tensor | None     # [blocks, kv_heads, head_dim, BLOCK_TOKENS]
+    v_pool: torch.Tensor | None     # [blocks, kv_heads, value_dim, BLOCK_TOKENS]
     writes: bool                    # False when the run reads another run's cache
     window: int | None
 
@@ -97,7 +97,7 @@ class SequenceCache:
             if kv_needs[run] is None or kv_needs[source] is None:
                 raise CacheError(f"run {run} reads the cache of run {source}, but one of them keeps no keys")
             a, b = kv_needs[run], kv_needs[source]
-            if (a.kv_heads, a.head_dim) != (b.kv_heads, b.head_dim):
+            if (a.kv_heads, a.head_dim, a.v_dim) != (b.kv_heads, b.head_dim, b.v_dim):
                 raise CacheError(f"run {run} reads the cache of run {source}, whose key/value shape differs")
             if b.window is not None and (a.window is None or a.window > b.window):
                 # the source's group gives blocks back by the source's window; a reader that looks
@@ -120,7 +120,8 @@ class SequenceCache:
 
         if self.device is not None:
             for group in self.kv_groups:
-                shape = (len(group.runs), 2, self.num_blocks, group.need.kv_heads * BLOCK_TOKENS * group.need.head_dim)
+                per_block = group.need.kv_heads * BLOCK_TOKENS
+                shape = (len(group.runs), self.num_blocks * per_block * (group.need.head_dim + group.need.v_dim))
                 # zeros, not empty: a tensor-core product multiplies the unused tail of a block by a
                 # probability of exactly zero, which must not meet a NaN left in fresh memory
                 group.storage = torch.zeros(shape, dtype=dtype, device=self.device)
@@ -193,8 +194,9 @@ class SequenceCache:
         k = v = None
         if g.storage is not None:
             need = g.need
-            k = g.storage[index, 0].view(self.num_blocks, need.kv_heads, BLOCK_TOKENS, need.head_dim)
-            v = g.storage[index, 1].view(self.num_blocks, need.kv_heads, need.head_dim, BLOCK_TOKENS)
+            keys = self.num_blocks * need.kv_heads * BLOCK_TOKENS * need.head_dim
+            k = g.storage[index, :keys].view(self.num_blocks, need.kv_heads, BLOCK_TOKENS, need.head_dim)
+            v = g.storage[index, keys:].view(self.num_blocks, need.kv_heads, need.v_dim, BLOCK_TOKENS)
         return RunCache(group, k, v, self._cache_from[run] is None, g.need.window)
 
     def run_state(self, run: int) -> list[torch.Tensor]:

@@ -1,11 +1,13 @@
 """Typed configurations and the architecture registry."""
 from .base import ConfigError, read_config_json
+from .famalorn import FamalornConfig
 from .llama import LlamaConfig, RopeScaling
 from .registry import Architecture, load_config, register_architecture, resolve_architecture, supported_architectures
 
 __all__ = [
     "Architecture",
     "ConfigError",
+    "FamalornConfig",
     "LlamaConfig",
     "RopeScaling",
     "load_config",

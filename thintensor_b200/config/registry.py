@@ -3,8 +3,8 @@ function that describes its model.
 
 The reference finds an architecture by comparing a compacted ``model_type`` or
 ``architectures[0]`` with alias substrings (thinruntime/architectures.py:385-399,
-thinruntime/model_arch.py:666-696).  Here ``architectures[0]`` is looked up exactly,
-and the compacted ``model_type`` is the fallback.
+thinruntime/model_arch.py:666-696).  Here ``architectures[0]`` (or a single
+``architecture``) is looked up exactly, and the compacted ``model_type`` is the fallback.
 """
 from __future__ import annotations
 
@@ -45,6 +45,8 @@ def resolve_architecture(raw: dict[str, Any]) -> Architecture:
     _load_builtin()
     raw = text_config(raw)
     names = raw.get("architectures") or []
+    if not names and isinstance(raw.get("architecture"), str):      # some designs name theirs in the singular
+        names = [raw["architecture"]]
     if names and names[0] in _ARCHITECTURES:
         return _ARCHITECTURES[names[0]]
     model_type = _compact(str(raw.get("model_type") or ""))

@@ -17,6 +17,10 @@ __device__ __forceinline__ float dot16(const T* __restrict__ krow, const float* 
 template <>
 __device__ __forceinline__ float dot16<float>(const float* __restrict__ krow, const float* __restrict__ q, int head_dim) {
     float acc = 0.0f;
+    if (head_dim & 3) {                     // rows that are not whole 16-byte pieces
+        for (int d = 0; d < head_dim; ++d) acc = fmaf(krow[d], q[d], acc);
+        return acc;
+    }
     for (int d = 0; d < head_dim; d += 4) {
         const float4 k = *reinterpret_cast<const float4*>(krow + d);
         acc = fmaf(k.x, q[d], acc);
@@ -30,6 +34,10 @@ __device__ __forceinline__ float dot16<float>(const float* __restrict__ krow, co
 template <>
 __device__ __forceinline__ float dot16<__nv_bfloat16>(const __nv_bfloat16* __restrict__ krow, const float* __restrict__ q, int head_dim) {
     float acc = 0.0f;
+    if (head_dim & 7) {                     // rows that are not whole 16-byte pieces
+        for (int d = 0; d < head_dim; ++d) acc = fmaf(__bfloat162float(krow[d]), q[d], acc);
+        return acc;
+    }
     for (int d = 0; d < head_dim; d += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -44,11 +52,15 @@ __device__ __forceinline__ float dot16<__nv_bfloat16>(const __nv_bfloat16* __res
 }
 
 // window <= 0: all keys 0..pos.  window > 0: keys pos - window + 1 .. pos.
+// Keys have head_dim numbers, values value_dim (the output's width per head).
+// sinks (float32, one per query head, or null): the softmax denominator also holds exp(sink_h), a
+// term that has no key and no value, is not multiplied by scale, and is counted once (by slice 0).
 template <typename T>
 __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,
                                       const T* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                                       int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before,
-                                      int sequences, int n_tokens, int heads, int kv_heads, int head_dim, float scale,
+                                      int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                                      float scale, const float* __restrict__ sinks,
                                       int window, int splits, T* __restrict__ out, float* __restrict__ part_acc,
                                       float* __restrict__ part_ml, unsigned* status) {
     tt_pdl_launch_dependents();
@@ -76,6 +88,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
     const int end = min(begin + per, pos + 1);
 
     float m_run = -INFINITY, l_run = 0.0f;
+    if (sinks && split == 0) { m_run = __ldg(sinks + h); l_run = 1.0f; }
     float acc[ATTN_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.0f;
@@ -88,7 +101,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
             off = tt_cache_offset(table_row, key, kh, kv_heads, head_dim, pool_blocks, status);
             if (off >= 0) {
                 score = dot16<T>(k_pool + off, qs, head_dim);
-                voff = tt_value_offset(table_row, key, kh, kv_heads, head_dim, pool_blocks, nullptr);
+                voff = tt_value_offset(table_row, key, kh, kv_heads, value_dim, pool_blocks, nullptr);
             }
         }
         const float m_tile = tt_warp_max(score);
@@ -109,7 +122,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 #pragma unroll
             for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(pj, tt_to_float(vcol[(size_t)d * TT_BLOCK_TOKENS]), acc[i]);
+                if (d < value_dim) acc[i] = fmaf(pj, tt_to_float(vcol[(size_t)d * TT_BLOCK_TOKENS]), acc[i]);
             }
         }
     }
@@ -119,14 +132,14 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < head_dim) out[((size_t)t * heads + h) * head_dim + d] = tt_from_float<T>(acc[i] * inv);
+            if (d < value_dim) out[((size_t)t * heads + h) * value_dim + d] = tt_from_float<T>(acc[i] * inv);
         }
     } else {
         const size_t slot = ((size_t)t * heads + h) * splits + split;
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < head_dim) part_acc[slot * head_dim + d] = acc[i];
+            if (d < value_dim) part_acc[slot * value_dim + d] = acc[i];
         }
         if (lane == 0) {
             part_ml[slot * 2] = m_run;

@@ -61,10 +61,11 @@ extern "C" int tt_embed_gather(const void* table, int table_dtype, const int* to
 }
 
 // ------------------------------------------------------------------------------------
-// residual add + RMSNorm.
+// residual add + RMSNorm, or + weight-only layer norm (centered != 0).
 //   x = residual[r] + delta[0][r] + delta[1][r] + ...      (fixed order)
 //   residual[r] = x                                        (only when rows == nullptr)
 //   out[i] = x * rsqrt(mean(x^2) + eps) * (weight + weight_offset)
+//   centered: out[i] = (x - mean(x)) * rsqrt(mean((x - mean(x))^2) + eps) * (weight + weight_offset) [+ bias]
 // One block per output row; the row is kept in shared memory between the two passes.
 // With `rows`, output row i is taken from residual row rows[i] and nothing is written
 // back (the final norm at the wanted positions).
@@ -73,7 +74,7 @@ template <typename TOut>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits,
                                    size_t split_stride, const float* __restrict__ weight, float weight_offset,
                                    float eps, TOut* __restrict__ out, const int* __restrict__ rows, int hidden,
-                                   int row_cache) {
+                                   int row_cache, int centered, const float* __restrict__ bias) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ float row_shared[];  // row_cache floats, then 32 for the reduction
@@ -82,29 +83,35 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     const int r = rows ? rows[i] : i;
     float* res = residual + (size_t)r * hidden;
     const float* del = delta ? delta + (size_t)r * hidden : nullptr;
-    float sumsq = 0.0f;
+    float sumsq = 0.0f, sum = 0.0f;
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float x = res[j];
         for (int s = 0; s < splits; ++s) x += del[(size_t)s * split_stride + j];
         if (j < row_cache) row_shared[j] = x;
         if (!rows && splits > 0) res[j] = x;
         sumsq += x * x;
+        sum += x;
     }
-    const float total = tt_block_sum(sumsq, reduce);
+    // the value of element j again: from shared memory, from the stream this thread has just written, or summed anew
+    auto again = [&](int j) {
+        if (j < row_cache) return row_shared[j];
+        float x = res[j];
+        if (rows) for (int s = 0; s < splits; ++s) x += del[(size_t)s * split_stride + j];
+        return x;
+    };
+    float mean = 0.0f, total;
+    if (centered) {
+        mean = tt_block_sum(sum, reduce) / (float)hidden;
+        float dev = 0.0f;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) { const float d = again(j) - mean; dev += d * d; }
+        total = tt_block_sum(dev, reduce);
+    } else {
+        total = tt_block_sum(sumsq, reduce);
+    }
     const float rstd = rsqrtf(total / (float)hidden + eps);
     TOut* o = out + (size_t)i * hidden;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-        float x;
-        if (j < row_cache) {
-            x = row_shared[j];
-        } else if (!rows) {
-            x = res[j];  // written back above by this same thread
-        } else {
-            x = res[j];
-            for (int s = 0; s < splits; ++s) x += del[(size_t)s * split_stride + j];
-        }
-        o[j] = tt_from_float<TOut>(x * rstd * (weight[j] + weight_offset));
-    }
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+        o[j] = tt_from_float<TOut>((again(j) - mean) * rstd * (weight[j] + weight_offset) + (bias ? bias[j] : 0.0f));
 }
 
 // four consecutive outputs as one store (the row start is 16-byte aligned and j counts groups of four)
@@ -129,7 +136,7 @@ template <typename TOut, int PIECES, int BATCH>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
                        const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
-                       const int* __restrict__ rows, int hidden) {
+                       const int* __restrict__ rows, int hidden, int centered, const float* __restrict__ bias) {
     tt_pdl_launch_dependents();
     __shared__ float reduce[32];
     const int i = blockIdx.x;
@@ -148,7 +155,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
     const float4* del = delta ? reinterpret_cast<const float4*>(delta + (size_t)r * hidden) : nullptr;
     const size_t stride4 = split_stride >> 2;
     float4 x[PIECES];
-    float sumsq = 0.0f;
+    float sumsq = 0.0f, sum = 0.0f;
 #pragma unroll
     for (int v = 0; v < PIECES; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
@@ -168,29 +175,49 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
             if (!rows && splits > 0) res[j] = a;
             x[v] = a;
             sumsq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            sum += (a.x + a.y) + (a.z + a.w);
         }
     }
-    const float total = tt_block_sum(sumsq, reduce);
+    float total;
+    if (centered) {                                           // the deviations from the mean, squared, in a pass of their own
+        const float mean = tt_block_sum(sum, reduce) / (float)hidden;
+        float dev = 0.0f;
+#pragma unroll
+        for (int v = 0; v < PIECES; ++v) {
+            const int j = threadIdx.x + v * blockDim.x;
+            if (j < quads) {
+                x[v].x -= mean; x[v].y -= mean; x[v].z -= mean; x[v].w -= mean;
+                dev += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+            }
+        }
+        total = tt_block_sum(dev, reduce);
+    } else {
+        total = tt_block_sum(sumsq, reduce);
+    }
     const float rstd = rsqrtf(total / (float)hidden + eps);
     TOut* o = out + (size_t)i * hidden;
 #pragma unroll
     for (int v = 0; v < PIECES; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
         if (j < quads) {
-            const float y0 = x[v].x * rstd * (w[v].x + weight_offset), y1 = x[v].y * rstd * (w[v].y + weight_offset);
-            const float y2 = x[v].z * rstd * (w[v].z + weight_offset), y3 = x[v].w * rstd * (w[v].w + weight_offset);
+            float y0 = x[v].x * rstd * (w[v].x + weight_offset), y1 = x[v].y * rstd * (w[v].y + weight_offset);
+            float y2 = x[v].z * rstd * (w[v].z + weight_offset), y3 = x[v].w * rstd * (w[v].w + weight_offset);
+            if (bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias) + j);
+                y0 += b.x; y1 += b.y; y2 += b.z; y3 += b.w;
+            }
             tt_store4(o + 4 * j, y0, y1, y2, y3);
         }
     }
 }
 
-extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, long long split_stride,
-                              const float* weight, float weight_offset, float eps, void* out, int out_dtype,
-                              const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+static int add_norm(float* residual, const float* delta, int splits, long long split_stride,
+                    const float* weight, float weight_offset, float eps, void* out, int out_dtype,
+                    const int* rows, int n_rows, int hidden, int centered, const float* bias, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (!delta) splits = 0;
     if (hidden % 4 == 0 && hidden <= 4096 * NORM_VEC_MAX && split_stride % 4 == 0 && ((uintptr_t)residual & 15) == 0 &&
-        ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)bias & 15) == 0) {
         int threads = ((hidden / 4 + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         if (n_rows >= 1024) {
@@ -201,7 +228,7 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
             if (threads > 1024) threads = 1024;
         }
         const bool one_piece = threads * 4 >= hidden;         // the block covers the row: one piece per thread, eight slices at a time
-#define TT_NORM(T, P, B) tt_launch_pdl(add_rmsnorm_vec_kernel<T, P, B>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (T*)out, rows, hidden)
+#define TT_NORM(T, P, B) tt_launch_pdl(add_rmsnorm_vec_kernel<T, P, B>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (T*)out, rows, hidden, centered, bias)
         if (out_dtype == TT_F32) { if (one_piece) TT_NORM(float, 1, 8); else TT_NORM(float, NORM_VEC_MAX, 2); }
         else { if (one_piece) TT_NORM(__nv_bfloat16, 1, 8); else TT_NORM(__nv_bfloat16, NORM_VEC_MAX, 2); }
 #undef TT_NORM
@@ -211,10 +238,23 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
     const int row_cache = hidden <= 11264 ? hidden : 11264;  // 44 KB of the default 48 KB
     const size_t shared = (size_t)(row_cache + 32) * sizeof(float);
     if (out_dtype == TT_F32)
-        tt_launch_pdl(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden, row_cache);
+        tt_launch_pdl(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden, row_cache, centered, bias);
     else
-        tt_launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden, row_cache);
+        tt_launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden, row_cache, centered, bias);
     TT_LAUNCH_CHECK();
+}
+
+extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, long long split_stride,
+                              const float* weight, float weight_offset, float eps, void* out, int out_dtype,
+                              const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+    return add_norm(residual, delta, splits, split_stride, weight, weight_offset, eps, out, out_dtype, rows, n_rows, hidden, 0, nullptr, stream);
+}
+
+// the same with the mean taken off first (layer norm); bias (float32, or null) is added at the end
+extern "C" int tt_add_layernorm(float* residual, const float* delta, int splits, long long split_stride,
+                                const float* weight, const float* bias, float eps, void* out, int out_dtype,
+                                const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+    return add_norm(residual, delta, splits, split_stride, weight, 0.0f, eps, out, out_dtype, rows, n_rows, hidden, 1, bias, stream);
 }
 
 // ------------------------------------------------------------------------------------
@@ -455,6 +495,106 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
 }
 
 // ------------------------------------------------------------------------------------
+// The general form of the kernel above, for attention whose queries and keys are normalised per head,
+// whose rotation pairs neighbouring numbers, or whose values have another size than its keys.
+//   proj: float32 [splits][tokens][cols]; q heads start at column 0, k heads at q_cols, v heads behind them
+//         (head_dim numbers per q and k head, value_dim per v head).
+//   norm: q_norm / k_norm (float32 [head_dim], or null for none) multiply x / sqrt(mean(x^2) + norm_eps) per head,
+//         before the rotation.
+//   rotation of the first rotary_dim numbers of a head by angle inv_freq[i] * float(position):
+//         interleaved != 0 pairs (2i, 2i + 1), else (i, i + rotary_dim / 2).
+// One warp per (token, head); the head's numbers pass through the warp's piece of shared memory.
+// ------------------------------------------------------------------------------------
+constexpr int QK_WARPS = 4;
+
+template <typename TAct>
+__global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int splits, size_t split_stride, int cols,
+                                           const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps,
+                                           const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
+                                           float attention_scaling, TAct* __restrict__ q_out, TAct* __restrict__ k_pool,
+                                           TAct* __restrict__ v_pool, const int* __restrict__ table, int table_width,
+                                           int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before,
+                                           int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                                           int write_cache, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float head_shared[];          // QK_WARPS * max(head_dim, value_dim)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int items = heads + (write_cache ? 2 * kv_heads : 0);
+    const long long w = (long long)blockIdx.x * QK_WARPS + warp;
+    if (w >= (long long)n_tokens * items) return;
+    const int t = (int)(w / items), item = (int)(w - (long long)t * items);
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    const int* table_row = table + (size_t)b * table_width;
+    const float* row = proj + (size_t)t * cols;
+    const int q_cols = heads * head_dim, k_cols = kv_heads * head_dim;
+    if (item >= heads + kv_heads) {                 // a value head: to the transposed pool as it is
+        const int kh = item - heads - kv_heads;
+        const long long off = tt_value_offset(table_row, pos, kh, kv_heads, value_dim, pool_blocks, status);
+        if (off < 0) return;
+        for (int d = lane; d < value_dim; d += 32)
+            v_pool[off + (long long)d * TT_BLOCK_TOKENS] = tt_from_float<TAct>(sum_slices(row + q_cols + k_cols + kh * value_dim + d, splits, split_stride));
+        return;
+    }
+    const bool is_q = item < heads;
+    const int head = is_q ? item : item - heads;
+    const float* src = row + (is_q ? head * head_dim : q_cols + head * head_dim);
+    const float* norm = is_q ? q_norm : k_norm;
+    float* x = head_shared + warp * max(head_dim, value_dim);
+    float sumsq = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) {
+        const float v = sum_slices(src + d, splits, split_stride);
+        x[d] = v;
+        sumsq += v * v;
+    }
+    if (norm) {
+        const float r = rsqrtf(tt_warp_sum(sumsq) / (float)head_dim + norm_eps);
+        __syncwarp();
+        for (int d = lane; d < head_dim; d += 32) x[d] = x[d] * r * __ldg(norm + d);
+    }
+    __syncwarp();
+    TAct* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * q_cols + (size_t)head * head_dim;
+    } else {
+        const long long off = tt_cache_offset(table_row, pos, head, kv_heads, head_dim, pool_blocks, status);
+        if (off < 0) return;
+        dst = k_pool + off;
+    }
+    const int half = rotary_dim >> 1;
+    for (int i = lane; i < half; i += 32) {
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        float si, co;
+        sincosf(__ldg(inv_freq + i) * (float)pos, &si, &co);
+        co *= attention_scaling;
+        si *= attention_scaling;
+        const float a = x[ia], c = x[ib];
+        dst[ia] = tt_from_float<TAct>(a * co - c * si);
+        dst[ib] = tt_from_float<TAct>(c * co + a * si);
+    }
+    for (int d = rotary_dim + lane; d < head_dim; d += 32) dst[d] = tt_from_float<TAct>(x[d]);
+}
+
+extern "C" int tt_qk_norm_rope_append(const float* proj, int splits, long long split_stride, int cols, const float* q_norm,
+                                      const float* k_norm, float norm_eps, const float* inv_freq, int rotary_dim, int interleaved,
+                                      float attention_scaling, void* q_out, void* k_pool, void* v_pool, int act_dtype,
+                                      const int* table, int table_width, int pool_blocks, const int* cu, const int* len_before,
+                                      int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                                      int write_cache, unsigned* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim || head_dim <= 0 || value_dim <= 0) return (int)cudaErrorInvalidValue;
+    const long long warps = (long long)n_tokens * (heads + (write_cache ? 2 * kv_heads : 0));
+    const unsigned blocks = (unsigned)((warps + QK_WARPS - 1) / QK_WARPS);
+    const size_t shared = (size_t)QK_WARPS * (head_dim > value_dim ? head_dim : value_dim) * sizeof(float);
+    if (act_dtype == TT_F32)
+        tt_launch_pdl(qk_norm_rope_append_kernel<float>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, status);
+    else
+        tt_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, status);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
 // What every layer's rotation of a step has in common, computed once per step: for packed token t
 // its position p = len_before[b] + (t - cu[b]), its sequence b, and cos and sin of inv_freq[i] * p
 // (float32 angle, as in the kernels above).  The tensor-core qkv product's epilogue reads these
@@ -487,12 +627,19 @@ extern "C" int tt_rope_table(const float* inv_freq, int half, const int* cu, con
 }
 
 // ------------------------------------------------------------------------------------
-// SwiGLU: act[t, j] = silu(gate[t, j]) * up[t, j], silu(g) = g / (1 + exp(-g)).
+// Gated unit: act[t, j] = f(gate[t, j]) * up[t, j].  f by `activation`: 0 silu(g) = g / (1 + exp(-g)),
+// 1 relu, 2 the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
 // gate_up: float32 [splits][tokens][2 * inter], gate columns first.
 // ------------------------------------------------------------------------------------
+__device__ __forceinline__ float tt_gate_activation(float g, int activation) {
+    if (activation == 1) return fmaxf(g, 0.0f);
+    if (activation == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+
 template <typename TAct>
 __global__ void swiglu_kernel(const float* __restrict__ gate_up, int splits, size_t split_stride,
-                              TAct* __restrict__ act, int inter, size_t total) {
+                              TAct* __restrict__ act, int inter, size_t total, int activation) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -506,19 +653,19 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, int splits, siz
         g += __ldg(row + s * split_stride + j);
         u += __ldg(row + s * split_stride + inter + j);
     }
-    act[idx] = tt_from_float<TAct>(g / (1.0f + expf(-g)) * u);
+    act[idx] = tt_from_float<TAct>(tt_gate_activation(g, activation) * u);
 }
 
 extern "C" int tt_swiglu(const float* gate_up, int splits, long long split_stride, void* act,
-                         int act_dtype, int n_tokens, int inter, cudaStream_t stream) {
+                         int act_dtype, int n_tokens, int inter, int activation, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (act_dtype == TT_F32)
-        tt_launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (float*)act, inter, total);
+        tt_launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (float*)act, inter, total, activation);
     else
-        tt_launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (__nv_bfloat16*)act, inter, total);
+        tt_launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (__nv_bfloat16*)act, inter, total, activation);
     TT_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,421 @@
+// Kernels of the recurrent token mixers: the short causal convolution with its carried inputs, the
+// Mamba-2 state-space recurrence, the gated delta-rule recurrence, the gated group norm behind both,
+// and the weighted sum of two branches.  Everything here is float32: inputs are the float32 partial
+// sums of a projection ([splits][tokens][cols], summed on the way in), states live in float32 and are
+// carried per sequence slot, and only the normalised output that feeds the next matrix product is
+// narrowed to the activation dtype.
+//
+// Packed batches: token t belongs to the sequence b with cu[b] <= t < cu[b + 1]; its state lies at
+// slots[b].  A recurrence walks a sequence's tokens in order and starts from the slot's state, so a
+// prompt cut into steps, a prompt and its decoded tokens, and a sequence inside a batch all run the
+// same chain of operations and give the same bits.
+//
+// A state matrix is owned column by column: the column of value dimension p (all its N state rows)
+// belongs to a group of REC_LANES neighbouring lanes, lane l holding rows l, l + REC_LANES, ... in
+// registers.  Row products with the token's vectors (read from shared memory, where a chunk of tokens
+// is staged) are summed inside the group with shuffles.  Columns are independent, so a CTA takes
+// REC_COLS of them for one (sequence, head) and the grid is heads x sequences x column tiles.
+#include "common.cuh"
+
+constexpr int REC_LANES = 8;        // lanes that share one state column
+constexpr int REC_COLS = 32;        // state columns of a CTA (REC_COLS * REC_LANES threads)
+constexpr int REC_CHUNK = 16;       // tokens staged in shared memory at a time
+constexpr int REC_MAX_ROWS = 256;   // largest state size per column (N of Mamba-2, key size of the delta rule)
+constexpr int CONV_MAX_TAPS = 8;
+
+__device__ __forceinline__ float rec_sum_slices(const float* __restrict__ p, int splits, size_t split_stride) {
+    float total = 0.0f;
+    for (int s = 0; s < splits; ++s) total += __ldg(p + (size_t)s * split_stride);
+    return total;
+}
+
+__device__ __forceinline__ float rec_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float rec_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+__device__ __forceinline__ float rec_group_sum(float v) {
+#pragma unroll
+    for (int o = REC_LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------
+// Causal convolution over time, one filter per channel:
+//   y[t, c] = f(bias[c] + sum_j w[c, j] * x[t - (taps - 1) + j, c]),   f = silu or identity.
+// x before this step's first token comes from the sequence's state, which holds its last taps - 1
+// inputs (oldest first, [taps - 1][channels]; zero for a new sequence).
+// Prompts: one kernel computes the outputs, a second one moves the states on (a thread per sequence
+// and channel), because the outputs of a sequence's first tokens read the state that the update
+// overwrites.  One token per sequence: a thread per (sequence, channel) does both.
+// ------------------------------------------------------------------------------------
+__global__ void causal_conv_kernel(const float* __restrict__ proj, int splits, size_t split_stride, int cols, int col_off,
+                                   int channels, const float* __restrict__ weight, const float* __restrict__ bias, int taps,
+                                   int activation, const float* __restrict__ state, size_t slot_stride, float* __restrict__ out,
+                                   const int* __restrict__ cu, const int* __restrict__ slots, int sequences, int n_tokens) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int first = cu[b];
+    const int i = t - first;
+    const float* st = state + (size_t)slots[b] * slot_stride;
+    float acc = bias ? __ldg(bias + c) : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int s = i - (taps - 1) + j;
+        const float x = s >= 0 ? rec_sum_slices(proj + (size_t)(first + s) * cols + col_off + c, splits, split_stride)
+                               : st[(size_t)(taps - 1 + s) * channels + c];
+        acc = fmaf(__ldg(weight + (size_t)c * taps + j), x, acc);
+    }
+    out[(size_t)t * channels + c] = activation ? rec_silu(acc) : acc;
+}
+
+// compute != 0: the sequence brings one token, whose output is computed here too
+__global__ void causal_conv_state_kernel(const float* __restrict__ proj, int splits, size_t split_stride, int cols, int col_off,
+                                         int channels, const float* __restrict__ weight, const float* __restrict__ bias, int taps,
+                                         int activation, float* __restrict__ state, size_t slot_stride, float* __restrict__ out,
+                                         const int* __restrict__ cu, const int* __restrict__ slots, int compute) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int first = cu[b], n = cu[b + 1] - first;
+    if (n <= 0) return;
+    float* st = state + (size_t)slots[b] * slot_stride;
+    const int keep = taps - 1;
+    float next[CONV_MAX_TAPS];
+    // the last `keep` entries of (old state, then this step's inputs)
+#pragma unroll
+    for (int e = 0; e < CONV_MAX_TAPS; ++e) {
+        if (e < keep) {
+            const int idx = n + e;              // index into the concatenation
+            next[e] = idx < keep ? st[(size_t)idx * channels + c]
+                                 : rec_sum_slices(proj + (size_t)(first + idx - keep) * cols + col_off + c, splits, split_stride);
+        }
+    }
+    if (compute) {
+        float acc = bias ? __ldg(bias + c) : 0.0f;
+        for (int j = 0; j < keep; ++j) acc = fmaf(__ldg(weight + (size_t)c * taps + j), st[(size_t)j * channels + c], acc);
+        const float x = rec_sum_slices(proj + (size_t)first * cols + col_off + c, splits, split_stride);
+        acc = fmaf(__ldg(weight + (size_t)c * taps + keep), x, acc);
+        out[(size_t)first * channels + c] = activation ? rec_silu(acc) : acc;
+    }
+#pragma unroll
+    for (int e = 0; e < CONV_MAX_TAPS; ++e)
+        if (e < keep) st[(size_t)e * channels + c] = next[e];
+}
+
+extern "C" int tt_causal_conv(const float* proj, int splits, long long split_stride, int cols, int col_off, int channels,
+                              const float* weight, const float* bias, int taps, int activation, float* state,
+                              long long slot_stride, float* out, const int* cu, const int* slots, int sequences, int n_tokens,
+                              int one_token_each, cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return 0;
+    const int threads = 128;
+    const unsigned bx = (unsigned)((channels + threads - 1) / threads);
+    if (taps < 1 || taps > CONV_MAX_TAPS || bx > 65535) return (int)cudaErrorInvalidValue;
+    if (!one_token_each) {
+        tt_launch_pdl(causal_conv_kernel, dim3(n_tokens, bx), dim3(threads), 0, stream, proj, splits, (size_t)split_stride, cols, col_off,
+                      channels, weight, bias, taps, activation, (const float*)state, (size_t)slot_stride, out, cu, slots, sequences, n_tokens);
+    }
+    if (taps > 1 || one_token_each)
+        tt_launch_pdl(causal_conv_state_kernel, dim3(sequences, bx), dim3(threads), 0, stream, proj, splits, (size_t)split_stride, cols,
+                      col_off, channels, weight, bias, taps, activation, state, (size_t)slot_stride, out, cu, slots, one_token_each);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Mamba-2 recurrence.  Per head h (group g = h / (heads / groups)), state S [N x P], token t:
+//   dt = softplus(dt_raw[t, h] + dt_bias[h])            (no clamp)
+//   S  = exp(-exp(A_log[h]) * dt) * S + dt * B[t, g] x[t, h]^T
+//   y[t, h] = S^T C[t, g] + D[h] * x[t, h]
+// xbc: float32 [tokens][inner + 2 * groups * N] (x, then B, then C: the convolution's output);
+// dt_raw: column dt_col of the projection's partial sums; state: [slots][heads][P][N].
+// ------------------------------------------------------------------------------------
+template <int K>
+__global__ void __launch_bounds__(REC_COLS* REC_LANES)
+mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __restrict__ proj, int splits, size_t split_stride,
+                   int cols, int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                   const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
+                   const int* __restrict__ cu, const int* __restrict__ slots, int heads, int P, int N, int groups) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float rec_shared[];
+    float* Bs = rec_shared;                          // [REC_CHUNK][N]
+    float* Cs = Bs + REC_CHUNK * N;                  // [REC_CHUNK][N]
+    float* xs = Cs + REC_CHUNK * N;                  // [REC_CHUNK][REC_COLS]
+    float* decay = xs + REC_CHUNK * REC_COLS;        // [REC_CHUNK]
+    float* step = decay + REC_CHUNK;                 // [REC_CHUNK]
+    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
+    const int first = cu[b], n = cu[b + 1] - first;
+    if (n <= 0) return;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    const int lane = threadIdx.x % REC_LANES, col = threadIdx.x / REC_LANES;
+    const int p = p0 + col;
+    const bool live = p < P;
+    float* S = state + (((size_t)slots[b] * heads + h) * P + (live ? p : 0)) * N;
+    float s[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        const int r = lane + i * REC_LANES;
+        s[i] = (live && r < N) ? S[r] : 0.0f;
+    }
+    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), skip = __ldg(d_skip + h);
+    for (int c0 = 0; c0 < n; c0 += REC_CHUNK) {
+        const int count = min(REC_CHUNK, n - c0);
+        __syncthreads();                             // the chunk before is done with
+        for (int e = threadIdx.x; e < count * N; e += blockDim.x) {
+            const int k = e / N, r = e - k * N;
+            const float* row = xbc + (size_t)(first + c0 + k) * xbc_cols;
+            Bs[k * N + r] = row[inner + g * N + r];
+            Cs[k * N + r] = row[inner + groups * N + g * N + r];
+        }
+        for (int e = threadIdx.x; e < count * REC_COLS; e += blockDim.x) {
+            const int k = e / REC_COLS, q = e - k * REC_COLS;
+            xs[e] = (p0 + q < P) ? xbc[(size_t)(first + c0 + k) * xbc_cols + h * P + p0 + q] : 0.0f;
+        }
+        if (threadIdx.x < count) {
+            const float raw = rec_sum_slices(proj + (size_t)(first + c0 + threadIdx.x) * cols + dt_col + h, splits, split_stride);
+            const float dt = rec_softplus(raw + bias);
+            step[threadIdx.x] = dt;
+            decay[threadIdx.x] = expf(neg_a * dt);
+        }
+        __syncthreads();
+        for (int k = 0; k < count; ++k) {
+            const float a = decay[k], x = xs[k * REC_COLS + col];
+            const float dx = step[k] * x;
+            const float* Bk = Bs + k * N;
+            const float* Ck = Cs + k * N;
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const int r = lane + i * REC_LANES;
+                if (r < N) {
+                    s[i] = fmaf(dx, Bk[r], a * s[i]);
+                    part = fmaf(s[i], Ck[r], part);
+                }
+            }
+            part = rec_group_sum(part);
+            if (lane == 0 && live) y[(size_t)(first + c0 + k) * inner + h * P + p] = fmaf(skip, x, part);
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const int r = lane + i * REC_LANES;
+            if (r < N) S[r] = s[i];
+        }
+    }
+}
+
+extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
+                              int dt_col, const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
+                              const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups,
+                              cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (N <= 0 || N > REC_MAX_ROWS || P <= 0 || groups <= 0 || heads % groups || sequences > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid(heads, sequences, (P + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
+    const size_t shared = (size_t)(2 * REC_CHUNK * N + REC_CHUNK * REC_COLS + 2 * REC_CHUNK) * sizeof(float);
+#define TT_SCAN(K) tt_launch_pdl(mamba2_scan_kernel<K>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups)
+    if (N <= 8 * REC_LANES) TT_SCAN(8);
+    else if (N <= 16 * REC_LANES) TT_SCAN(16);
+    else TT_SCAN(32);
+#undef TT_SCAN
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Gated delta rule.  Per head h (query/key head g = h / (heads / qk_heads)), state S [D x V], token t:
+//   q = q / sqrt(sum(q^2) + 1e-6) * D^-1/2,   k = k / sqrt(sum(k^2) + 1e-6)       (per head)
+//   beta = sigmoid(b_raw[t, h]),   decay = exp(-exp(A_log[h]) * softplus(a_raw[t, h] + dt_bias[h]))
+//   S = decay * S;  u = beta * (v - S^T k);  S = S + k u^T;  o[t, h] = S^T q
+// qkv: float32 [tokens][2 * qk_heads * D + heads * V] (q, k, v: the convolutions' output); b_raw and
+// a_raw: columns b_col + h and a_col + h of the projection's partial sums; state: [slots][heads][V][D].
+// ------------------------------------------------------------------------------------
+template <int K>
+__global__ void __launch_bounds__(REC_COLS* REC_LANES)
+delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __restrict__ proj, int splits, size_t split_stride,
+                  int cols, int b_col, int a_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                  float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slots,
+                  int heads, int qk_heads, int D, int V) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float rec_shared[];
+    float* qs = rec_shared;                          // [REC_CHUNK][D]
+    float* ks = qs + REC_CHUNK * D;                  // [REC_CHUNK][D]
+    float* vs = ks + REC_CHUNK * D;                  // [REC_CHUNK][REC_COLS]
+    float* decay = vs + REC_CHUNK * REC_COLS;        // [REC_CHUNK]
+    float* beta = decay + REC_CHUNK;                 // [REC_CHUNK]
+    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
+    const int first = cu[b], n = cu[b + 1] - first;
+    if (n <= 0) return;
+    const int g = h / (heads / qk_heads);
+    const int lane = threadIdx.x % REC_LANES, col = threadIdx.x / REC_LANES;
+    const int warp = threadIdx.x >> 5, wlane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int p = p0 + col;
+    const bool live = p < V;
+    float* S = state + (((size_t)slots[b] * heads + h) * V + (live ? p : 0)) * D;
+    float s[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        const int r = lane + i * REC_LANES;
+        s[i] = (live && r < D) ? S[r] : 0.0f;
+    }
+    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), q_scale = rsqrtf((float)D);
+    const int k_off = qk_heads * D, v_off = 2 * qk_heads * D;
+    for (int c0 = 0; c0 < n; c0 += REC_CHUNK) {
+        const int count = min(REC_CHUNK, n - c0);
+        __syncthreads();
+        // a warp per (token, q or k): load, sum of squares, scale to unit length
+        for (int item = warp; item < 2 * count; item += warps) {
+            const int k = item >> 1, is_k = item & 1;
+            const float* src = qkv + (size_t)(first + c0 + k) * qkv_cols + (is_k ? k_off : 0) + g * D;
+            float* dst = (is_k ? ks : qs) + k * D;
+            float sumsq = 0.0f;
+            for (int r = wlane; r < D; r += 32) {
+                const float v = src[r];
+                dst[r] = v;
+                sumsq += v * v;
+            }
+            const float scale = rsqrtf(tt_warp_sum(sumsq) + 1e-6f) * (is_k ? 1.0f : q_scale);
+            __syncwarp();
+            for (int r = wlane; r < D; r += 32) dst[r] *= scale;
+        }
+        for (int e = threadIdx.x; e < count * REC_COLS; e += blockDim.x) {
+            const int k = e / REC_COLS, q = e - k * REC_COLS;
+            vs[e] = (p0 + q < V) ? qkv[(size_t)(first + c0 + k) * qkv_cols + v_off + h * V + p0 + q] : 0.0f;
+        }
+        if (threadIdx.x < count) {
+            const float* row = proj + (size_t)(first + c0 + threadIdx.x) * cols;
+            const float braw = rec_sum_slices(row + b_col + h, splits, split_stride);
+            const float araw = rec_sum_slices(row + a_col + h, splits, split_stride);
+            beta[threadIdx.x] = 1.0f / (1.0f + expf(-braw));
+            decay[threadIdx.x] = expf(neg_a * rec_softplus(araw + bias));
+        }
+        __syncthreads();
+        for (int k = 0; k < count; ++k) {
+            const float a = decay[k];
+            const float* qk = qs + k * D;
+            const float* kk = ks + k * D;
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const int r = lane + i * REC_LANES;
+                if (r < D) {
+                    s[i] *= a;
+                    part = fmaf(s[i], kk[r], part);
+                }
+            }
+            const float u = beta[k] * (vs[k * REC_COLS + col] - rec_group_sum(part));
+            part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const int r = lane + i * REC_LANES;
+                if (r < D) {
+                    s[i] = fmaf(kk[r], u, s[i]);
+                    part = fmaf(s[i], qk[r], part);
+                }
+            }
+            part = rec_group_sum(part);
+            if (lane == 0 && live) o[(size_t)(first + c0 + k) * (heads * V) + h * V + p] = part;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const int r = lane + i * REC_LANES;
+            if (r < D) S[r] = s[i];
+        }
+    }
+}
+
+extern "C" int tt_delta_scan(const float* qkv, int qkv_cols, const float* proj, int splits, long long split_stride, int cols,
+                             int b_col, int a_col, const float* dt_bias, const float* a_log, float* state, float* o,
+                             const int* cu, const int* slots, int sequences, int heads, int qk_heads, int D, int V,
+                             cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (D <= 0 || D > REC_MAX_ROWS || V <= 0 || qk_heads <= 0 || heads % qk_heads || sequences > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid(heads, sequences, (V + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
+    const size_t shared = (size_t)(2 * REC_CHUNK * D + REC_CHUNK * REC_COLS + 2 * REC_CHUNK) * sizeof(float);
+#define TT_SCAN(K) tt_launch_pdl(delta_scan_kernel<K>, grid, block, shared, stream, qkv, qkv_cols, proj, splits, (size_t)split_stride, cols, b_col, a_col, dt_bias, a_log, state, o, cu, slots, heads, qk_heads, D, V)
+    if (D <= 8 * REC_LANES) TT_SCAN(8);
+    else if (D <= 16 * REC_LANES) TT_SCAN(16);
+    else TT_SCAN(32);
+#undef TT_SCAN
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Gate and group norm behind a recurrence.  y: float32 [tokens][width], cut into groups of `group`
+// neighbouring columns; gate: columns gate_col .. gate_col + width - 1 of a projection's partial sums.
+//   gate_first != 0:  v = y * silu(gate);  out = v / sqrt(mean_group(v^2) + eps) * w
+//   gate_first == 0:  out = y / sqrt(mean_group(y^2) + eps) * w * silu(gate)
+// w (float32 [weight_len]) is indexed by column modulo weight_len: one weight for the whole width, or one
+// per position inside a head that all heads share.  One block per (token, group).
+// ------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int width, int group, const float* __restrict__ proj,
+                                        int splits, size_t split_stride, int cols, int gate_col,
+                                        const float* __restrict__ weight, int weight_len, float eps, int gate_first,
+                                        TOut* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    __shared__ float reduce[32];
+    const int groups = width / group;
+    const int t = blockIdx.x / groups, gi = blockIdx.x - t * groups;
+    const float* yr = y + (size_t)t * width + (size_t)gi * group;
+    const float* gr = proj + (size_t)t * cols + gate_col + (size_t)gi * group;
+    float sumsq = 0.0f;
+    for (int j = threadIdx.x; j < group; j += blockDim.x) {
+        float v = yr[j];
+        if (gate_first) v *= rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+        sumsq += v * v;
+    }
+    const float r = rsqrtf(tt_block_sum(sumsq, reduce) / (float)group + eps);
+    TOut* o = out + (size_t)t * width + (size_t)gi * group;
+    for (int j = threadIdx.x; j < group; j += blockDim.x) {
+        const float gate = rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+        const float w = __ldg(weight + (gi * group + j) % weight_len);
+        const float v = gate_first ? yr[j] * gate * r * w : yr[j] * r * w * gate;
+        o[j] = tt_from_float<TOut>(v);
+    }
+}
+
+extern "C" int tt_gated_group_norm(const float* y, int n_tokens, int width, int group, const float* proj, int splits,
+                                   long long split_stride, int cols, int gate_col, const float* weight, int weight_len, float eps,
+                                   int gate_first, void* out, int out_dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (group <= 0 || width % group || weight_len <= 0) return (int)cudaErrorInvalidValue;
+    const long long blocks = (long long)n_tokens * (width / group);
+    if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
+    const int threads = group >= 2048 ? 256 : (group >= 256 ? 128 : (group > 32 ? 64 : 32));
+    if (out_dtype == TT_F32)
+        tt_launch_pdl(gated_group_norm_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out);
+    else
+        tt_launch_pdl(gated_group_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// out[i] = wa * sum_s a[s][i] + wb * sum_s b[s][i]: two branches' outputs (each the partial sums of a
+// product) weighted and added, float32.
+// ------------------------------------------------------------------------------------
+__global__ void weighted_pair_kernel(const float* __restrict__ a, int a_splits, size_t a_stride, float wa,
+                                     const float* __restrict__ b, int b_splits, size_t b_stride, float wb,
+                                     float* __restrict__ out, size_t total) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    out[i] = wa * rec_sum_slices(a + i, a_splits, a_stride) + wb * rec_sum_slices(b + i, b_splits, b_stride);
+}
+
+extern "C" int tt_weighted_pair(const float* a, int a_splits, long long a_stride, float wa, const float* b, int b_splits,
+                                long long b_stride, float wb, float* out, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    tt_launch_pdl(weighted_pair_kernel, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, stream, a, a_splits,
+                  (size_t)a_stride, wa, b, b_splits, (size_t)b_stride, wb, out, (size_t)total);
+    TT_LAUNCH_CHECK();
+}

@@ -50,10 +50,15 @@ class DecoderModel:
             built: dict[str, BuiltPart] = {}
             for role, registry_name in arrangement_cls.roles.items():
                 if role not in layer.parts:
+                    if role in arrangement_cls.optional:
+                        continue
                     raise ValueError(f"arrangement {layer.arrangement!r} needs a part for role {role!r}")
                 built[role] = _build(REGISTRIES[registry_name], layer.parts[role])
+            unknown = set(layer.parts) - set(arrangement_cls.roles)
+            if unknown:
+                raise ValueError(f"arrangement {layer.arrangement!r} has no role {sorted(unknown)[0]!r}")
             self._layer_parts.append(built)
-            self.layers.append(arrangement_cls({role: b.part for role, b in built.items()}))
+            self.layers.append(arrangement_cls({role: b.part for role, b in built.items()}, **dict(layer.params)))
         self.bound = False
         self.device_driven = False
         self.cache_needs()          # sets self.users

@@ -188,6 +188,62 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
     _check(fn(_ptr(residual), _ptr(delta), splits, stride, _ptr(weight), weight_offset, eps, _ptr(out), dtype_code(out.dtype), _ptr(rows), n_rows, hidden, _stream()), "add_rmsnorm")
 
 
+def add_layernorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
+                  out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """residual += sum(delta over its first axis); out = (x - mean) / sqrt(var + eps) * weight (+ bias), the
+    variance being the mean squared deviation.  ``rows`` as for :func:`add_rmsnorm`."""
+    _need(residual, torch.float32, "residual")
+    _need(weight, torch.float32, "norm weight")
+    if bias is not None:
+        _need(bias, torch.float32, "norm bias")
+    if not out.is_contiguous():
+        raise KernelError("norm output must be contiguous")
+    hidden = residual.shape[-1]
+    splits, stride = 0, 0
+    if delta is not None:
+        _need(delta, torch.float32, "delta")
+        splits, stride = delta.shape[0], delta.stride(0)
+    n_rows = rows.numel() if rows is not None else residual.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    fn = _fn("elementwise", "tt_add_layernorm", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta), splits, stride, _ptr(weight), _ptr(bias), eps, _ptr(out), dtype_code(out.dtype), _ptr(rows), n_rows, hidden, _stream()), "add_layernorm")
+
+
+def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, norm_eps: float,
+                        inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool, attention_scaling: float, q_out: torch.Tensor,
+                        k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, table: torch.Tensor, cu: torch.Tensor,
+                        len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
+                        value_dim: int, status: torch.Tensor) -> None:
+    """The general form of :func:`rope_append`: float32 partial sums ``proj`` [splits, tokens, cols] hold q heads, then k
+    heads (``head_dim`` numbers each), then v heads (``value_dim`` each).  q and k are normalised per head (x / rms(x) *
+    weight; ``q_norm`` / ``k_norm`` float32 [head_dim] or None), then their first ``rotary_dim`` numbers are rotated, in
+    neighbouring pairs (``interleaved``) or in halves; q goes to ``q_out``, k and v to the block pools.  Without pools
+    the projection holds queries only."""
+    _need(proj, torch.float32, "projection")
+    _need(inv_freq, torch.float32, "inv_freq")
+    write = k_pool is not None
+    cols = heads * head_dim + (kv_heads * (head_dim + value_dim) if write else 0)
+    if proj.shape[-1] != cols:
+        raise KernelError(f"the projection has {proj.shape[-1]} columns, expected {cols}")
+    for norm in (q_norm, k_norm):
+        if norm is not None:
+            _need(norm, torch.float32, "query/key norm weight")
+            if norm.numel() != head_dim:
+                raise KernelError(f"a query/key norm weight must have {head_dim} numbers")
+    if write and (k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype):
+        raise KernelError("cache pools and activations must share a dtype")
+    if rotary_dim and inv_freq.numel() < rotary_dim // 2:
+        raise KernelError("the rotary table is shorter than half the rotary part")
+    fn = _fn("elementwise", "tt_qk_norm_rope_append", [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                                                       c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(proj), proj.shape[0], proj.stride(0), cols, _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(inv_freq), rotary_dim,
+              1 if interleaved else 0, attention_scaling, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), dtype_code(q_out.dtype), _ptr(table),
+              table.shape[1], k_pool.shape[0] if write else 0, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim,
+              value_dim, 1 if write else 0, _ptr(status), _stream()), "qk_norm_rope_append")
+
+
 def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, q_out: torch.Tensor,
                 k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, table: torch.Tensor | None, cu: torch.Tensor,
                 len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
@@ -225,12 +281,19 @@ def rope_table(inv_freq: torch.Tensor, rotary_dim: int, cu: torch.Tensor, len_be
     _check(fn(_ptr(inv_freq), half, _ptr(cu), _ptr(len_before), sequences, n_tokens, _ptr(cos_sin), _ptr(where), _stream()), "rope_table")
 
 
-def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """act = silu(gate) * up from float32 partial sums [splits, tokens, 2 * inter]."""
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor, activation: str = "silu") -> None:
+    """act = f(gate) * up from float32 partial sums [splits, tokens, 2 * inter]; f is silu, relu or the
+    tanh form of gelu."""
     _need(gate_up, torch.float32, "gate_up")
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"gate activation {activation!r} is not one of {sorted(GATE_ACTIVATIONS)}")
     inter = gate_up.shape[-1] // 2
-    fn = _fn("elementwise", "tt_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(gate_up), gate_up.shape[0], gate_up.stride(0), _ptr(act), dtype_code(act.dtype), gate_up.shape[1], inter, _stream()), "swiglu")
+    fn = _fn("elementwise", "tt_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), gate_up.shape[0], gate_up.stride(0), _ptr(act), dtype_code(act.dtype), gate_up.shape[1], inter,
+              GATE_ACTIVATIONS[activation], _stream()), "swiglu")
 
 
 def copy_int32(dst: torch.Tensor, src: torch.Tensor, extra: torch.Tensor | None = None) -> None:
@@ -257,24 +320,33 @@ def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int, cou
 
 # --------------------------------------------------------------------------- attention
 def check_head_dim(head_dim: int) -> None:
-    if head_dim <= 0 or head_dim % 16 or head_dim > MAX_HEAD_DIM:
-        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to {MAX_HEAD_DIM}, not {head_dim}")
+    if head_dim <= 0 or head_dim > MAX_HEAD_DIM:
+        raise KernelError(f"attention kernels take head sizes up to {MAX_HEAD_DIM}, not {head_dim}")
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
               len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
-              part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
-    """Exact causal attention of ``n_tokens`` packed query tokens over the block cache."""
+              part_ml: torch.Tensor | None, status: torch.Tensor, value_dim: int | None = None,
+              sinks: torch.Tensor | None = None) -> None:
+    """Exact causal attention of ``n_tokens`` packed query tokens over the block cache.  ``value_dim``: the size of a
+    value head where it differs from the keys'.  ``sinks`` (float32, one per query head): a term exp(sink) in the
+    softmax denominator that has no key and no value and is not scaled."""
     check_head_dim(head_dim)
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    check_head_dim(value_dim)
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != heads:
+            raise KernelError(f"attention with {heads} query heads needs {heads} sinks, got {sinks.numel()}")
     if heads % kv_heads:
         raise KernelError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
         raise KernelError("queries, cache and output must share a dtype")
     fn = _fn("attention", "tt_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu),
-              _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, scale, window, splits, _ptr(out),
+              _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, _ptr(sinks), window, splits, _ptr(out),
               _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
 
 
@@ -388,6 +460,106 @@ def attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, heads, kv_heads, head_dim, scale, window, _ptr(out), _ptr(status), _stream()), "attention_tcgen05")
+
+
+# --------------------------------------------------------------------------- recurrent
+def _projection(proj: torch.Tensor) -> tuple:
+    """(pointer, splits, split stride, columns) of float32 partial sums [splits, tokens, cols]."""
+    _need(proj, torch.float32, "projection")
+    if proj.dim() != 3:
+        raise KernelError("a projection's partial sums are [splits, tokens, cols]")
+    return _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2]
+
+
+def causal_conv(proj: torch.Tensor, col_off: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None, activation: bool,
+                state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, n_tokens: int,
+                one_token_each: bool) -> None:
+    """out[t, c] = f(bias[c] + sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over each sequence's tokens, x being
+    columns ``col_off .. col_off + channels`` of ``proj``; inputs before the step's first token come from ``state``
+    [slots, taps - 1, channels] (float32, oldest first), which is moved on to the step's last inputs.  f is silu
+    (``activation``) or the identity."""
+    _need(weight, torch.float32, "convolution weight")
+    _need(state, torch.float32, "convolution state")
+    _need(out, torch.float32, "convolution output")
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or tuple(state.shape[1:]) != (taps - 1, channels) or tuple(out.shape) != (n_tokens, channels):
+        raise KernelError(f"convolution: weight {tuple(weight.shape)}, state {tuple(state.shape)}, out {tuple(out.shape)} do not fit {channels} channels")
+    if bias is not None:
+        _need(bias, torch.float32, "convolution bias")
+    p, splits, stride, cols = _projection(proj)
+    if col_off < 0 or col_off + channels > cols:
+        raise KernelError("convolution: the channels lie outside the projection")
+    fn = _fn("recurrent", "tt_causal_conv", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                             c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(p, splits, stride, cols, col_off, channels, _ptr(weight), _ptr(bias), taps, 1 if activation else 0, _ptr(state),
+              state.stride(0) if state.numel() else 0, _ptr(out), _ptr(cu), _ptr(slots), sequences, n_tokens, 1 if one_token_each else 0,
+              _stream()), "causal_conv", (0 if one_token_each else 1) + (1 if taps > 1 or one_token_each else 0))
+
+
+def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+                state: torch.Tensor, y: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, heads: int,
+                head_dim: int, state_size: int, groups: int) -> None:
+    """The Mamba-2 recurrence over each sequence's tokens.  ``xbc`` float32 [tokens, inner + 2 * groups * state_size]
+    holds x, B and C; column ``dt_col + h`` of ``proj`` the raw step size of head h; ``state`` float32
+    [slots, heads, head_dim, state_size]; ``y`` float32 [tokens, inner] receives S^T C + D x."""
+    inner = heads * head_dim
+    for t, name in ((xbc, "x/B/C"), (dt_bias, "dt_bias"), (a_log, "A_log"), (d_skip, "D"), (state, "recurrent state"), (y, "recurrence output")):
+        _need(t, torch.float32, name)
+    if xbc.shape[1] != inner + 2 * groups * state_size or tuple(state.shape[1:]) != (heads, head_dim, state_size) or y.shape[1] != inner:
+        raise KernelError("mamba2_scan: shapes do not fit the sizes")
+    p, splits, stride, cols = _projection(proj)
+    fn = _fn("recurrent", "tt_mamba2_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(xbc), xbc.shape[1], p, splits, stride, cols, dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(y),
+              _ptr(cu), _ptr(slots), sequences, heads, head_dim, state_size, groups, _stream()), "mamba2_scan")
+
+
+def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, heads: int, qk_heads: int,
+               key_dim: int, value_dim: int) -> None:
+    """The gated delta rule over each sequence's tokens.  ``qkv`` float32 [tokens, 2 * qk_heads * key_dim + heads *
+    value_dim] holds q, k, v (q and k are made unit vectors here, q also times key_dim^-1/2); columns ``b_col + h`` and
+    ``a_col + h`` of ``proj`` the raw write strength and decay input of head h; ``state`` float32
+    [slots, heads, value_dim, key_dim]; ``out`` float32 [tokens, heads * value_dim] receives S^T q."""
+    for t, name in ((qkv, "q/k/v"), (dt_bias, "dt_bias"), (a_log, "A_log"), (state, "recurrent state"), (out, "recurrence output")):
+        _need(t, torch.float32, name)
+    if (qkv.shape[1] != 2 * qk_heads * key_dim + heads * value_dim or tuple(state.shape[1:]) != (heads, value_dim, key_dim)
+            or out.shape[1] != heads * value_dim):
+        raise KernelError("delta_scan: shapes do not fit the sizes")
+    p, splits, stride, cols = _projection(proj)
+    fn = _fn("recurrent", "tt_delta_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], p, splits, stride, cols, b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(out),
+              _ptr(cu), _ptr(slots), sequences, heads, qk_heads, key_dim, value_dim, _stream()), "delta_scan")
+
+
+def gated_group_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, gate_first: bool,
+                     out: torch.Tensor) -> None:
+    """Groups of ``group`` neighbouring columns of ``y`` (float32 [tokens, width]) divided by their root mean square,
+    times ``weight`` (indexed by column modulo its length), with the gate silu(columns ``gate_col ..`` of ``proj``)
+    multiplied in before the norm (``gate_first``) or after it."""
+    _need(y, torch.float32, "norm input")
+    _need(weight, torch.float32, "norm weight")
+    tokens, width = y.shape
+    if tuple(out.shape) != (tokens, width) or not out.is_contiguous() or width % group:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    p, splits, stride, cols = _projection(proj)
+    if gate_col + width > cols:
+        raise KernelError("gated_group_norm: the gate lies outside the projection")
+    fn = _fn("recurrent", "tt_gated_group_norm", [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
+                                                  c_float, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(y), tokens, width, group, p, splits, stride, cols, gate_col, _ptr(weight), weight.numel(), eps, 1 if gate_first else 0,
+              _ptr(out), dtype_code(out.dtype), _stream()), "gated_group_norm")
+
+
+def weighted_pair(a: torch.Tensor, wa: float, b: torch.Tensor, wb: float, out: torch.Tensor) -> None:
+    """out = wa * sum(a over its first axis) + wb * sum(b over its first axis), all float32."""
+    for t, name in ((a, "first branch"), (b, "second branch"), (out, "sum")):
+        _need(t, torch.float32, name)
+    if a.shape[1:] != b.shape[1:] or out.numel() != a[0].numel():
+        raise KernelError("weighted_pair: shapes differ")
+    fn = _fn("recurrent", "tt_weighted_pair", [c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float, c_void_p, c_longlong, c_void_p])
+    _check(fn(_ptr(a), a.shape[0], a.stride(0), wa, _ptr(b), b.shape[0], b.stride(0), wb, _ptr(out), out.numel(), _stream()), "weighted_pair")
 
 
 # -------------------------------------------------------------------------------- gemm

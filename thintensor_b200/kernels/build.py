@@ -36,6 +36,7 @@ SOURCES: dict[str, list[str]] = {
     "gemm_tcgen05": [],
     "attention_mma": [],
     "attention_tcgen05": [],
+    "recurrent": [],
 }
 
 

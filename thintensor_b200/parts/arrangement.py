@@ -10,12 +10,24 @@ norm kernel a read of the product and a write of the stream); the delta is then 
 """
 from __future__ import annotations
 
+import torch
+
+from ..kernels import api
 from .base import ARRANGEMENTS, Arrangement, Delta
 
 
 @ARRANGEMENTS.register("pre_norm")
 class PreNorm(Arrangement):
+    """A layer without a feed-forward leaves out ``ffn_norm`` and ``ffn``: its mixer's output is then what the next
+    layer's norm adds."""
+
     roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
+    optional = ("ffn_norm", "ffn")
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        if ("ffn" in parts) != ("ffn_norm" in parts):
+            raise ValueError("a pre-norm layer has a feed-forward and its norm, or neither")
 
     def mixers(self):
         return [self.parts["mixer"]]
@@ -31,5 +43,45 @@ class PreNorm(Arrangement):
         normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
         self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
         mixed = self.parts["mixer"].forward(ctx, normed, caches[0], states[0])
+        if "ffn" not in self.parts:
+            return mixed
+        self.parts["ffn_norm"].forward(ctx, residual, mixed, normed)
+        return self.parts["ffn"].forward(ctx, normed)
+
+
+@ARRANGEMENTS.register("pre_norm_pair")
+class PreNormPair(Arrangement):
+    """Two mixers side by side on the same normed input, ``h += left_scale * left(norm(h)) + right_scale *
+    right(norm(h))``, then the feed-forward sublayer (if the layer has one).  Each mixer has a cache and states of
+    its own.  The weighted sum is formed in float32 from the two output projections' partial sums."""
+
+    roles = {"mixer_norm": "norm", "left": "mixer", "right": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
+    optional = ("ffn_norm", "ffn")
+
+    def __init__(self, parts, left_scale: float = 1.0, right_scale: float = 1.0):
+        super().__init__(parts)
+        if ("ffn" in parts) != ("ffn_norm" in parts):
+            raise ValueError("a pre-norm layer has a feed-forward and its norm, or neither")
+        self.left_scale, self.right_scale = float(left_scale), float(right_scale)
+
+    def mixers(self):
+        return [self.parts["left"], self.parts["right"]]
+
+    def device_driven(self) -> bool:
+        return all(part.device_driven() for part in self.parts.values())
+
+    def run(self, ctx, residual, pending: Delta | None, caches, states) -> Delta:
+        hidden = residual.shape[-1]
+        normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
+        self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
+        ctx.residual = None                 # the branches' outputs are weighted before they reach the stream
+        left = self.parts["left"].forward(ctx, normed, caches[0], states[0])
+        right = self.parts["right"].forward(ctx, normed, caches[1], states[1])
+        both = ctx.scratch("block.pair", (1, ctx.n_tokens, hidden), torch.float32)
+        api.weighted_pair(left.tensor, self.left_scale, right.tensor, self.right_scale, both)
+        mixed = Delta(both)
+        if "ffn" not in self.parts:
+            return mixed
+        ctx.residual = residual
         self.parts["ffn_norm"].forward(ctx, residual, mixed, normed)
         return self.parts["ffn"].forward(ctx, normed)

@@ -4,8 +4,16 @@ For each token: q, k, v projections of the normed hidden state (one fused matrix
 position encoding on q and k, k and v appended to the sequence's cache, softmax
 attention of q over every cached key of its sequence (or the last ``window`` of them)
 with query head h reading key/value head ``h // (heads / kv_heads)`` and scores scaled
-by ``head_dim ** -0.5``, then the output projection
+by ``head_dim ** -0.5`` (or ``scale``), then the output projection
 (thinruntime/gpu_runtime.py:10151-10249 and 8913-8961).
+
+Options beyond that form, each a parameter: value heads of another size than key heads
+(``value_dim``); queries and keys divided by their root mean square per head and multiplied
+by a weight of ``head_dim`` numbers that all heads share, before the rotation
+(``qk_norm_eps``); a learned number per query head whose exponential joins the softmax
+denominator without a key or a value (``sink``); a rotation that pairs neighbouring numbers
+(the position encoding's ``interleaved``).  A layer that uses any of them runs the general
+kernels: one that normalises, rotates and appends, and the exact attention.
 """
 from __future__ import annotations
 
@@ -31,12 +39,24 @@ def kv_splits(ctx, parallel_units: int, keys_per_slice: int, target_units: int) 
 
 @MIXERS.register("attention")
 class CausalAttention(Mixer):
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks"}
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec | None = None,
-                 bias: bool = False, window: int | None = None, scale: float | None = None):
+                 bias: bool = False, window: int | None = None, scale: float | None = None, value_dim: int | None = None,
+                 qk_norm_eps: float | None = None, sink: bool = False, names: dict | None = None):
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
         if self.heads % self.kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
         api.check_head_dim(self.head_dim)
+        self.value_dim = self.head_dim if value_dim is None else int(value_dim)
+        api.check_head_dim(self.value_dim)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.sink = bool(sink)
+        self.names = {**self.NAMES, **(names or {})}
+        self.q_norm: torch.Tensor | None = None
+        self.k_norm: torch.Tensor | None = None
+        self.sinks: torch.Tensor | None = None
         self.bias = bool(bias)
         self.window = None if not window else int(window)
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
@@ -52,12 +72,18 @@ class CausalAttention(Mixer):
     # -------------------------------------------------------------- declarations
     def weights(self) -> dict[str, WeightDecl]:
         q, kv = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        n = self.names
         out = {
-            "q_proj.weight": WeightDecl((q, self.hidden)),
-            "k_proj.weight": WeightDecl((kv, self.hidden)),
-            "v_proj.weight": WeightDecl((kv, self.hidden)),
-            "o_proj.weight": WeightDecl((self.hidden, q)),
+            n["q"]: WeightDecl((q, self.hidden)),
+            n["k"]: WeightDecl((kv, self.hidden)),
+            n["v"]: WeightDecl((self.kv_heads * self.value_dim, self.hidden)),
+            n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim)),
         }
+        if self.qk_norm_eps is not None:
+            out[n["q_norm"]] = WeightDecl((self.head_dim,), init="norm")
+            out[n["k_norm"]] = WeightDecl((self.head_dim,), init="norm")
+        if self.sink:
+            out[n["sink"]] = WeightDecl((self.heads,))
         if self.bias:
             out.update({
                 "q_proj.bias": WeightDecl((q,)), "k_proj.bias": WeightDecl((kv,)), "v_proj.bias": WeightDecl((kv,)),
@@ -66,7 +92,13 @@ class CausalAttention(Mixer):
         return out
 
     def cache_need(self) -> KVNeed:
-        return KVNeed(self.kv_heads, self.head_dim, self.window)
+        return KVNeed(self.kv_heads, self.head_dim, self.window, None if self.value_dim == self.head_dim else self.value_dim)
+
+    @property
+    def general(self) -> bool:
+        """Whether the layer needs the general kernels (see the module's text)."""
+        return (self.value_dim != self.head_dim or self.qk_norm_eps is not None or self.sink
+                or (self.rot is not None and self.rot.interleaved and self.rot.rotary_dim > 0))
 
     def bind(self, tensors, dtype, device) -> None:
         self.position.bind({}, dtype, device)
@@ -76,13 +108,21 @@ class CausalAttention(Mixer):
                 raise ValueError(f"the rotary part must be even and at most the head size {self.head_dim}, got {self.rot.rotary_dim}")
         else:
             self.rot = RotaryTable(torch.zeros(1, dtype=torch.float32, device=device), 0, 1.0)
-        weight = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0)
+        n = self.names
+        if self.general and self.bias:
+            raise ValueError("attention with a value size of its own, a query/key norm, a sink or an interleaved rotation takes no biases")
+        if self.qk_norm_eps is not None:
+            self.q_norm = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
+        if self.sink:
+            self.sinks = tensors[n["sink"]].to(torch.float32).contiguous()
+        weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0)
         bias = None
         if self.bias:
             bias = torch.cat([tensors["q_proj.bias"].float(), tensors["k_proj.bias"].float(), tensors["v_proj.bias"].float()])
         self.qkv = Linear(weight, bias)
         self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
-        self.out = Linear(tensors["o_proj.weight"], tensors["o_proj.bias"] if self.bias else None)
+        self.out = Linear(tensors[n["o"]], tensors["o_proj.bias"] if self.bias else None)
 
     def projections(self) -> list:
         return [self.qkv, self.out]             # q_only is a view of qkv's first rows
@@ -97,7 +137,20 @@ class CausalAttention(Mixer):
         table = ctx.tables[cache.group]
         q_cols = self.heads * self.head_dim
         rot = self.rot
-        mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
+        mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, self.heads * self.value_dim))
+        if self.general:
+            projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
+            q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
+            api.qk_norm_rope_append(projection, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq, rot.rotary_dim,
+                                    rot.interleaved, rot.attention_scaling, q, cache.k_pool if cache.writes else None,
+                                    cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
+                                    self.heads, self.kv_heads, self.head_dim, self.value_dim, ctx.status)
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
+            part_acc, part_ml = self.slice_scratch(ctx, splits)
+            api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+                          self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
+                          value_dim=self.value_dim, sinks=self.sinks)
+            return self.out.delta(ctx, mixed, "attention.out")
         if (cache.writes and not ctx.decode and x.dtype == torch.bfloat16
                 and api.gemm_tcgen05_qkv_rope_takes(x, self.qkv.weight, self.head_dim, rot.rotary_dim)):
             # long prompts: the qkv product's epilogue rotates, narrows and appends to the cache, so the float32
@@ -155,7 +208,7 @@ class CausalAttention(Mixer):
         """Where the slices of the keys leave their partial results (nothing for one slice)."""
         if splits <= 1:
             return None, None
-        return (ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.head_dim,), torch.float32),
+        return (ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.value_dim,), torch.float32),
                 ctx.scratch("attention.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32))
 
     def tickets(self, ctx, splits: int):

@@ -48,11 +48,16 @@ class WeightDecl:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values a mixer wants kept for each sequence: ``kv_heads`` heads of
-    ``head_dim`` numbers per token; ``window`` = only the last so many tokens."""
+    ``head_dim`` numbers per token (values: ``value_dim``, if given); ``window`` = only the last so many tokens."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None        # numbers per value head where they differ from the keys' (None: head_dim)
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -125,6 +130,7 @@ class RotaryTable:
     rotary_dim: int
     attention_scaling: float = 1.0
     signature: int = 0      # equal for tables with equal numbers (0: unknown): layers with equal tables can share what a step derives from them
+    interleaved: bool = False   # pairs are (2i, 2i + 1) instead of (i, i + rotary_dim / 2)
 
 
 class PositionEncoding(Part):
@@ -171,6 +177,7 @@ class Arrangement:
     the registry each comes from; ``run`` returns the delta still to be added."""
 
     roles: dict[str, str] = {}
+    optional: tuple[str, ...] = ()      # roles a layer may leave out
 
     def __init__(self, parts: dict[str, Part]):
         self.parts = parts

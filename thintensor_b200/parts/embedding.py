@@ -16,15 +16,16 @@ from .linear import Linear
 
 @EMBEDDINGS.register("table")
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab: int, hidden: int, scale: float = 1.0):
+    def __init__(self, vocab: int, hidden: int, scale: float = 1.0, name: str = "weight"):
         self.vocab, self.hidden, self.scale = int(vocab), int(hidden), float(scale)
+        self.name = name                        # what the checkpoint calls the table, behind the part's prefix
         self.table: torch.Tensor | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
-        return {"weight": WeightDecl((self.vocab, self.hidden))}
+        return {self.name: WeightDecl((self.vocab, self.hidden))}
 
     def bind(self, tensors, dtype, device) -> None:
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.name].contiguous()
 
     def device_driven(self) -> bool:
         return True
@@ -39,18 +40,20 @@ class LinearHead(Head):
     the checkpoint stores none (the embedding table); with ``tied`` it is used even if
     a head is stored."""
 
-    def __init__(self, hidden: int, vocab: int, fallback: str | None = None, tied: bool = False, bias: bool = False):
+    def __init__(self, hidden: int, vocab: int, fallback: str | None = None, tied: bool = False, bias: bool = False,
+                 name: str = "weight"):
         self.hidden, self.vocab, self.fallback, self.tied, self.bias = int(hidden), int(vocab), fallback, bool(tied), bool(bias)
+        self.name = name
         self.linear: Linear | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
-        out = {"weight": WeightDecl((self.vocab, self.hidden), alias_of=self.fallback, prefer_alias=self.tied)}
+        out = {self.name: WeightDecl((self.vocab, self.hidden), alias_of=self.fallback, prefer_alias=self.tied)}
         if self.bias:
             out["bias"] = WeightDecl((self.vocab,))
         return out
 
     def bind(self, tensors, dtype, device) -> None:
-        self.linear = Linear(tensors["weight"], tensors.get("bias"))
+        self.linear = Linear(tensors[self.name], tensors.get("bias"))
 
     def projections(self) -> list:
         return [self.linear]

@@ -1,24 +1,33 @@
-"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` with
-``silu(g) = g / (1 + exp(-g))`` (thinruntime/gpu_runtime.py:10286-10366; the activation
-at :10351 and thinruntime/triton_kernels.py:2760-2774)."""
+"""Dense gated feed-forward: ``down(f(gate(x)) * up(x))``, f = ``silu(g) = g / (1 + exp(-g))`` by default
+(thinruntime/gpu_runtime.py:10286-10366; the activation at :10351 and
+thinruntime/triton_kernels.py:2760-2774), or ``relu`` or ``gelu_tanh`` (``activation``).  ``names`` gives the
+checkpoint's names of the gate, up and down matrices behind the part's prefix."""
 from __future__ import annotations
 
+from ..kernels import api
 from .base import FEED_FORWARDS, Delta, FeedForward, WeightDecl
 from .linear import GatedLinear, Linear
 
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, hidden: int, inter: int, bias: bool = False):
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, hidden: int, inter: int, bias: bool = False, activation: str = "silu", names: dict | None = None):
         self.hidden, self.inter, self.bias = int(hidden), int(inter), bool(bias)
+        if activation not in api.GATE_ACTIVATIONS:
+            raise ValueError(f"gate activation {activation!r} is not one of {sorted(api.GATE_ACTIVATIONS)}")
+        self.activation = activation
+        self.names = {**self.NAMES, **(names or {})}
         self.gate_up: GatedLinear | None = None
         self.down: Linear | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
+        n = self.names
         out = {
-            "gate_proj.weight": WeightDecl((self.inter, self.hidden)),
-            "up_proj.weight": WeightDecl((self.inter, self.hidden)),
-            "down_proj.weight": WeightDecl((self.hidden, self.inter)),
+            n["gate"]: WeightDecl((self.inter, self.hidden)),
+            n["up"]: WeightDecl((self.inter, self.hidden)),
+            n["down"]: WeightDecl((self.hidden, self.inter)),
         }
         if self.bias:
             out.update({"gate_proj.bias": WeightDecl((self.inter,)), "up_proj.bias": WeightDecl((self.inter,)),
@@ -26,9 +35,10 @@ class SwiGLU(FeedForward):
         return out
 
     def bind(self, tensors, dtype, device) -> None:
-        self.gate_up = GatedLinear(tensors["gate_proj.weight"], tensors["up_proj.weight"],
-                                   tensors.get("gate_proj.bias"), tensors.get("up_proj.bias"))
-        self.down = Linear(tensors["down_proj.weight"], tensors.get("down_proj.bias"))
+        n = self.names
+        self.gate_up = GatedLinear(tensors[n["gate"]], tensors[n["up"]],
+                                   tensors.get("gate_proj.bias"), tensors.get("up_proj.bias"), self.activation)
+        self.down = Linear(tensors[n["down"]], tensors.get("down_proj.bias"))
 
     def projections(self) -> list:
         return [self.gate_up.fused, self.down]

@@ -79,10 +79,12 @@ class Linear:
 
 class GatedLinear:
     """gate and up projections as one ``[2 * inter, in]`` matrix (gate rows first) and
-    ``silu(gate) * up`` in the activation dtype."""
+    ``f(gate) * up`` in the activation dtype (f: silu, relu or gelu_tanh)."""
 
-    def __init__(self, gate: torch.Tensor, up: torch.Tensor, gate_bias: torch.Tensor | None, up_bias: torch.Tensor | None):
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, gate_bias: torch.Tensor | None, up_bias: torch.Tensor | None,
+                 activation: str = "silu"):
         self.inter = gate.shape[0]
+        self.activation = activation
         bias = None
         if gate_bias is not None or up_bias is not None:
             zeros = torch.zeros(self.inter, dtype=torch.float32, device=gate.device)
@@ -93,7 +95,7 @@ class GatedLinear:
         tokens = x.shape[0]
         act = ctx.scratch(name + ".act", (tokens, self.inter))
         w = self.fused
-        if w.bias is None and api.gemm_tcgen05_usable(x, w.weight) and (
+        if self.activation == "silu" and w.bias is None and api.gemm_tcgen05_usable(x, w.weight) and (
                 tokens > api.SKINNY_TOKENS or api.gemm_tcgen05_splits(tokens, 2 * self.inter, x.shape[1]) == 1):
             # the float32 gate/up never reach global memory.  With few tokens this form cannot cut k
             # into slices, so it is taken only where the plain product would not slice either
@@ -101,5 +103,5 @@ class GatedLinear:
             api.set_label(name)
             api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)
             return act
-        api.swiglu(w(ctx, x, name), act)
+        api.swiglu(w(ctx, x, name), act, self.activation)
         return act

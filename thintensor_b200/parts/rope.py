@@ -34,8 +34,12 @@ class RotaryEncoding(PositionEncoding):
     kind = "rotary"
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, scaling: dict | None = None,
-                 attention_scaling: float = 1.0):
+                 attention_scaling: float = 1.0, interleaved: bool = False, table_precision: str = "float32"):
         self.head_dim = int(head_dim)
+        self.interleaved = bool(interleaved)            # pairs (2i, 2i + 1) instead of (i, i + rotary_dim / 2)
+        if table_precision not in ("float32", "float64"):
+            raise ValueError(f"the frequency table is computed in float32 or float64, not {table_precision!r}")
+        self.table_precision = table_precision          # float64: computed in double and rounded to float32 once
         self.rotary_dim = self.head_dim if rotary_dim is None else int(rotary_dim)
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim must be even and within (0, head_dim]; got {self.rotary_dim} for head_dim {self.head_dim}")
@@ -46,8 +50,8 @@ class RotaryEncoding(PositionEncoding):
         self._rotary: RotaryTable | None = None
 
     def _table(self) -> torch.Tensor:
-        index = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
-        inv_freq = self.theta ** (-index / self.rotary_dim)
+        index = torch.arange(0, self.rotary_dim, 2, dtype=getattr(torch, self.table_precision))
+        inv_freq = (self.theta ** (-index / self.rotary_dim)).to(torch.float32)
         kind = (self.scaling or {}).get("rope_type", "default")
         if kind == "default":
             return inv_freq
@@ -59,7 +63,7 @@ class RotaryEncoding(PositionEncoding):
 
     def bind(self, tensors, dtype, device) -> None:
         signature = hash((self.inv_freq_host.numpy().tobytes(), self.rotary_dim)) or 1
-        self._rotary = RotaryTable(self.inv_freq_host.to(device), self.rotary_dim, self.attention_scaling, signature)
+        self._rotary = RotaryTable(self.inv_freq_host.to(device), self.rotary_dim, self.attention_scaling, signature, self.interleaved)
 
     def rotary(self) -> RotaryTable:
         if self._rotary is None:

@@ -29,10 +29,13 @@ class PartSpec:
 class LayerSpec:
     """One layer: an arrangement (how the parts are wired around the residual
     stream) and the parts by role.  The ``pre_norm`` arrangement has the roles
-    ``mixer_norm``, ``mixer``, ``ffn_norm`` and ``ffn``."""
+    ``mixer_norm``, ``mixer``, ``ffn_norm`` and ``ffn`` (the last two may be left out: a layer
+    without a feed-forward).  ``params`` are the arrangement's own constants (the weights with
+    which ``pre_norm_pair`` adds its two mixers, say)."""
 
     arrangement: str
     parts: Mapping[str, PartSpec]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
