@@ -135,9 +135,11 @@ def sink_attention(h, p, w, prefix, eps):
     v = (h @ w[prefix + "v"].T).reshape(T, G, V)
     q = rms(q, eps) * w[prefix + "q.norm"]
     k = rms(k, eps) * w[prefix + "k.norm"]
-    pos = torch.arange(T)
-    q = rotate_interleaved(q, pos, p["rot"]["dims"], p["rot"]["base"])
-    k = rotate_interleaved(k, pos, p["rot"]["dims"], p["rot"]["base"])
+    rot = p.get("rot")
+    if rot and rot["dims"]:
+        pos = torch.arange(T)
+        q = rotate_interleaved(q, pos, rot["dims"], rot["base"])
+        k = rotate_interleaved(k, pos, rot["dims"], rot["base"])
     out = torch.zeros(T, H, V, dtype=h.dtype)
     for head in range(H):
         g = head // (H // G)
