@@ -49,8 +49,22 @@ CONFIGS = {
                 "left_scale": 1.5, "right_scale": 0.5}},
         ],
     },
+    # key and value heads of 64 and of 128 numbers: the sizes the tensor-core attention kernels take in bfloat16
+    "t": {
+        "architecture": "Famalorn", "vocab": 160, "width": 128, "norm": {"eps": 1e-6},
+        "layers": [
+            {"type": "parallel", "mlp": {"kind": "dense", "ff": 192}, "mixer": {
+                "left": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"dims": 32, "base": 100000.0}},
+                "right": {"heads": 2, "vdim": 32, "state": 16, "groups": 1, "norm_groups": 1, "conv": 4},
+                "left_scale": 0.9, "right_scale": 1.1}},
+            {"type": "parallel", "mlp": None, "mixer": {
+                "left": {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 128, "scale": 0.09, "rot": {"dims": 128, "base": 10000.0}},
+                "right": {"heads": 4, "vdim": 16, "state": 32, "groups": 4, "norm_groups": 2, "conv": 3},
+                "left_scale": 1.2, "right_scale": 0.8}},
+        ],
+    },
 }
-SEEDS = {"p": 3, "r": 4, "s": 6}
+SEEDS = {"p": 3, "r": 4, "s": 6, "t": 8}
 
 
 def shape_weights(tensors: dict[str, torch.Tensor], seed: int, slow_decay: bool = False) -> dict[str, torch.Tensor]:

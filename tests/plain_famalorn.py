@@ -10,8 +10,9 @@ sublayers are weight-only layer norms.
 Everything here works on one whole sequence at a time, token by token where the
 mechanism is a recurrence, with no cache and no batching.  It shares no code with the
 package under test: own config reading, own safetensors reader, one function per
-mechanism.  Arithmetic is float64 throughout (``dtype``), so what it returns is the
-design's exact value up to the rounding of the stored weights.
+mechanism.  Arithmetic is float64 throughout (``dtype``) except for the rotation's angles
+(see ``rotate_interleaved``), so what it returns is the design's value up to the rounding of
+the stored weights.
 """
 from __future__ import annotations
 
@@ -116,10 +117,13 @@ def mamba2(h, p, w, prefix, eps):
 
 
 def rotate_interleaved(x, positions, dims, base):
-    """x [T, heads, dim]: pairs (2i, 2i+1) of the first ``dims`` numbers turn by p * base^(-2i/dims)."""
+    """x [T, heads, dim]: pairs (2i, 2i+1) of the first ``dims`` numbers turn by p * base^(-2i/dims).  The design
+    computes positions and angles in 32-bit floats, and at a far position an angle rounded there differs from the
+    exact one by more than the tests allow; so the frequency is rounded to float32 and so is its product with the
+    position, the one place where this file does not work in ``x.dtype``."""
     out = x.clone()
     for i in range(dims // 2):
-        a = positions.to(x.dtype) * base ** (-2.0 * i / dims)
+        a = (positions.to(torch.float32) * torch.tensor(base ** (-2.0 * i / dims), dtype=torch.float32)).to(x.dtype)
         c, s = torch.cos(a)[:, None], torch.sin(a)[:, None]
         u, v = x[:, :, 2 * i], x[:, :, 2 * i + 1]
         out[:, :, 2 * i] = u * c - v * s

@@ -257,8 +257,10 @@ def sink_attention_plain(q, k, v, sinks, scale, group):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("unit_norm", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rot,interleaved", [(4, 2, 32, 24, 16, True), (6, 1, 20, 36, 0, True), (3, 3, 16, 16, 16, True),
-                                                                     (6, 3, 128, 80, 64, True), (2, 1, 24, 24, 12, False)])
-def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_heads, dim, vdim, rot, interleaved):
+                                                                     (6, 3, 128, 80, 64, True), (2, 1, 24, 24, 12, False),
+                                                                     (8, 2, 64, 64, 32, True), (4, 1, 128, 128, 128, True)])
+@pytest.mark.parametrize("kernels", ["exact", "tensor"])
+def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_heads, dim, vdim, rot, interleaved, kernels):
     """Prompts go through the norm / rotation / append kernel into a scrambled cache and then attend; afterwards one token
     each is decoded with the keys cut into slices.  Head 1's sink is made to take nearly all of its weight.  With
     ``unit_norm`` (norm weights of one, under which norm and rotation commute) the key at position 3 of the longest
@@ -266,8 +268,10 @@ def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_hea
     two coincide and that one far key out of 700 dominates the head."""
     from thintensor_b200.kernels import api
 
+    if kernels == "tensor" and not (dim == vdim and api.attention_tcgen05_supports(dtype, heads, kv_heads, dim)):
+        pytest.skip("the tensor-core kernels take bfloat16 with key and value heads of 64 or 128")
     totals = [700, 1, 65, 128]
-    eps, scale, base = 1e-5, 1.0, 10000.0
+    eps, scale, base = 1e-5, min(1.0, 32.0 / dim), 10000.0       # scores of up to 32: the aligned far key stands out of 700 others
     group = heads // kv_heads
     k_pool, v_pool, table = build_cache([t + 1 for t in totals], kv_heads, dim, vdim, dtype, seed=80)
     q_norm = torch.ones(dim) if unit_norm else 1.0 + randn(dim, seed=81, scale=0.2)
@@ -283,7 +287,7 @@ def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_hea
             return t
         if interleaved:
             return plain.rotate_interleaved(t, positions, rot, base)
-        a = positions[:, None, None].double() * inv_freq.double()
+        a = (positions[:, None, None].float() * inv_freq).double()              # angles are float32 by definition
         lo, hi = t[..., : rot // 2], t[..., rot // 2: rot]
         return torch.cat([lo * torch.cos(a) - hi * torch.sin(a), hi * torch.cos(a) + lo * torch.sin(a), t[..., rot:]], -1)
 
@@ -303,12 +307,25 @@ def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_hea
         api.qk_norm_rope_append(slices(x, 2, 84).to(DEV), q_norm.to(DEV), k_norm.to(DEV), eps, inv_freq.to(DEV), rot, interleaved, 1.0, q_out,
                                 k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, vdim, status)
         out = torch.empty(tokens, heads * vdim, dtype=dtype, device=DEV)
-        splits = 5 if decode else 1
-        part_acc = torch.empty(tokens * heads * splits * vdim, dtype=torch.float32, device=DEV)
-        part_ml = torch.empty(tokens * heads * splits * 2, dtype=torch.float32, device=DEV)
-        api.attention(q_out, k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, scale, 0, splits, out, part_acc,
-                      part_ml, status, value_dim=vdim, sinks=sinks.to(DEV))
-        return out.double().cpu().reshape(tokens, heads, vdim)
+        if kernels == "tensor" and not decode:              # prompts: both products on the tcgen05 tensor cores
+            api.attention_tcgen05(q_out, k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, scale, 0, out, status,
+                                  sinks=sinks.to(DEV))
+            return out.double().cpu().reshape(tokens, heads, vdim)
+        results = []
+        for splits in ((1, 5, 11) if decode else (1,)):     # 11 slices: more than a cluster combines, so by tickets
+            part_acc = torch.empty(tokens * heads * splits * vdim, dtype=torch.float32, device=DEV)
+            part_ml = torch.empty(tokens * heads * splits * 2, dtype=torch.float32, device=DEV)
+            if kernels == "tensor":
+                tickets = torch.zeros(64, dtype=torch.int32, device=DEV) if splits > 8 else None
+                api.attention_mma(q_out, k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, scale, 0, splits, out,
+                                  part_acc, part_ml, status, one_token_each=True, tickets=tickets, sinks=sinks.to(DEV))
+            else:
+                api.attention(q_out, k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, scale, 0, splits, out,
+                              part_acc, part_ml, status, value_dim=vdim, sinks=sinks.to(DEV))
+            results.append(out.double().cpu().reshape(tokens, heads, vdim))
+        for other in results[1:]:                            # however the keys are cut, the sink counts once
+            assert float((other - results[0]).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2)
+        return results[-1]
 
     x = randn(sum(totals), cols, seed=85)
     last = randn(len(totals), cols, seed=86)

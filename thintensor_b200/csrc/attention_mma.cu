@@ -607,7 +607,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, int undelivered_bytes,
-                        unsigned* status) {
+                        unsigned* status, const float* __restrict__ sinks) {
     constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
     constexpr int TILE = TT_BLOCK_TOKENS * HD * 2;     // bytes of a block's keys of one head, and of its values
     extern __shared__ __align__(128) uint4 slots[];   // [WARPS][STAGES]: a K tile [64 keys][HD], then a V tile [HD][64 keys], as they lie in the cache
@@ -799,6 +799,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             }
         }
         const size_t row_index = (size_t)b * heads + kh * group + r;
+        if (sinks && split == 0) {
+            // the sink of this query head: one more term of the denominator, exp(sink), with no key, no value and no
+            // scale; it enters like the result of a warp that saw one key of that score and a value of zero
+            const float ms = __ldg(sinks + kh * group + r) * 1.4426950408889634f;
+            const float m2 = fmaxf(m, ms);
+            const float keep = m == -INFINITY ? 0.0f : exp2f(m - m2);
+            l = fmaf(l, keep, exp2f(ms - m2));
+            acc0 *= keep;
+            acc1 *= keep;
+            m = m2;
+        }
         if (splits == 1) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             *reinterpret_cast<__nv_bfloat162*>(out + row_index * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
@@ -855,7 +866,7 @@ inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; 
 template <int HD, bool ROPE, int SHAPE, int NQ>
 cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
-                                int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+                                int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
                                 cudaStream_t stream) {
     using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
@@ -871,7 +882,7 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
             }
             return tt_launch_pdl(with_tickets, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
                 (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
+                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
         }
     }
     static bool configured = false;
@@ -884,23 +895,23 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
     if (slices_form_cluster(splits))
         return tt_launch_pdl_cluster(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream, (unsigned)splits,
             (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
+            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
+        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
 }
 
 // One column tile of 8 queries serves groups of up to 8 query heads per key/value head, two serve up to 16.
 template <int HD, bool ROPE, int SHAPE = ONE_PER_SM>
 cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                           int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
-                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
                           cudaStream_t stream) {
     if (heads / kv_heads > 8)
         return launch_decode_tiles<HD, ROPE, SHAPE, 2>(q, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
-                                                       kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
+                                                       kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, sinks, stream);
     return launch_decode_tiles<HD, ROPE, SHAPE, 1>(q, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
-                                                   kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
+                                                   kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, sinks, stream);
 }
 
 template <int HD>
@@ -917,7 +928,7 @@ int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* par
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
-           int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+           int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
            cudaStream_t stream) {
     const int group = heads / kv_heads;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -936,19 +947,19 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             if (ctas > 2 * sm_count && ctas <= 3 * sm_count) {          // one wave of three CTAs per SM
                 err = launch_decode<HD, false, THREE_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
                                                              table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
-                                                             window, splits, out, part_acc, part_ml, tickets, status, stream);
+                                                             window, splits, out, part_acc, part_ml, tickets, status, sinks, stream);
                 done = true;
             } else if (ctas > sm_count) {                               // several waves
                 err = launch_decode<HD, false, TWO_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
                                                            table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
-                                                           window, splits, out, part_acc, part_ml, tickets, status, stream);
+                                                           window, splits, out, part_acc, part_ml, tickets, status, sinks, stream);
                 done = true;
             }
         }
         if (!done)
             err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
                                            pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
-                                           part_acc, part_ml, tickets, status, stream);
+                                           part_acc, part_ml, tickets, status, sinks, stream);
     } else {
         // packed prompts: keys are not sliced (a prompt has tiles enough); a CTA is 64 query rows
         if (splits != 1) return (int)cudaErrorInvalidValue;
@@ -998,13 +1009,14 @@ extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) 
 extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
                                 int heads, int kv_heads, int head_dim, float scale, int window, int splits,
-                                int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+                                int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
         return (int)cudaErrorInvalidValue;
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
-#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, tickets, status, stream)
+    if (sinks && !one_token_each) return (int)cudaErrorInvalidValue;      // sinks (one float per query head) join the decode kernel only
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, tickets, status, sinks, stream)
     switch (head_dim) {
         case 32: TT_LAUNCH(32);
         case 64: TT_LAUNCH(64);
@@ -1033,6 +1045,7 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
                                         int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
                                         cudaStream_t stream) {
     if (sequences <= 0) return 0;
+    const float* sinks = nullptr;           // layers with sinks run the separate rotation kernel
     if (!tt_attention_decode_rope_supports(heads, kv_heads, head_dim, rotary_dim) || splits < 1 || splits > 65535 || kv_heads > 65535 ||
         qkv_splits < 1 || split_stride % 4 != 0 || ((uintptr_t)qkv & 15) != 0)
         return (int)cudaErrorInvalidValue;
@@ -1040,7 +1053,7 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
     const DecodeRope rope{qkv, qkv_splits, (size_t)split_stride, inv_freq, attention_scaling, write_cache};
     const float scale_log2 = scale * 1.4426950408889634f;
     const cudaError_t err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences,
-                                                    heads, kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
+                                                    heads, kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, sinks, stream);
     if (err != cudaSuccess) return (int)err;
     return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits) || tickets);
 }

@@ -94,6 +94,7 @@ struct Args {
     int window;
     __nv_bfloat16* out;
     unsigned* status;
+    const float* sinks;     // one per query head, or null: exp(sink) joins the softmax denominator, with no key, no value and no scale
 };
 
 template <int HD>
@@ -346,6 +347,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int last = n_blocks - 1;
             if (!mbar_wait(smem_u32(&pv_done[last & 1]), (uint32_t)((last >> 1) & 1))) expired();
         }
+        if (args.sinks && half == 0 && row_ok) {
+            // l is the sum of 2^(score * scale_log2 - m_used); the sink's term in the same units
+            const int sink_head = kh * args.group + (r - local * args.group);
+            l += exp2f(__ldg(args.sinks + sink_head) * 1.4426950408889634f - (m_used == -INFINITY ? 0.0f : m_used));
+        }
         if (SPLIT == 2) {               // the row sum is the two threads' sums together (both rescaled to the same maximum)
             pair_max[n_blocks & 1][half][r] = l;
             pair_barrier();
@@ -424,7 +430,7 @@ extern "C" int tt_attention_tcgen05_supports(int heads, int kv_heads, int head_d
 // if the tensor maps could not be made.
 extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                     int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
-                                    int heads, int kv_heads, int head_dim, float scale, int window, void* out,
+                                    int heads, int kv_heads, int head_dim, float scale, const float* sinks, int window, void* out,
                                     unsigned* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_tcgen05_supports(heads, kv_heads, head_dim) || ((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
@@ -435,7 +441,7 @@ extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const voi
     args.tokens_per_tile = ROWS / args.group;
     args.cta_tiles = (n_tokens + args.tokens_per_tile - 1) / args.tokens_per_tile + sequences;   // upper bound; spare CTAs leave at once
     if (args.cta_tiles > 65535) return (int)cudaErrorInvalidValue;                               // the grid's y extent; steps are cut into pieces long before
-    args.scale_log2 = scale * 1.4426950408889634f; args.window = window; args.out = (__nv_bfloat16*)out; args.status = status;
+    args.scale_log2 = scale * 1.4426950408889634f; args.window = window; args.out = (__nv_bfloat16*)out; args.status = status; args.sinks = sinks;
     if (head_dim == 64) return launch<64>(q, k_pool, v_pool, args, n_tokens, stream);
     return launch<128>(q, k_pool, v_pool, args, n_tokens, stream);
 }

@@ -335,10 +335,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
     check_head_dim(head_dim)
     value_dim = head_dim if value_dim is None else int(value_dim)
     check_head_dim(value_dim)
-    if sinks is not None:
-        _need(sinks, torch.float32, "sinks")
-        if sinks.numel() != heads:
-            raise KernelError(f"attention with {heads} query heads needs {heads} sinks, got {sinks.numel()}")
+    _check_sinks(sinks, heads)
     if heads % kv_heads:
         raise KernelError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
@@ -354,6 +351,14 @@ def _attention_launches(splits: int, decode: bool, tickets: bool = False) -> int
     """Kernels one call launches: the decode kernel combines up to 8 slices itself (a thread-block
     cluster) and, given tickets, any number; otherwise more slices need the merge kernel."""
     return 1 if splits == 1 or (decode and (splits <= 8 or tickets)) else 2
+
+
+def _check_sinks(sinks: torch.Tensor | None, heads: int) -> None:
+    """``sinks``: float32, one per query head; exp(sink) joins the softmax denominator with no key, no value and no scale."""
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != heads:
+            raise KernelError(f"attention with {heads} query heads needs {heads} sinks, got {sinks.numel()}")
 
 
 def _check_tickets(tickets: torch.Tensor | None, sequences: int, kv_heads: int) -> None:
@@ -373,7 +378,7 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
                   len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
                   scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
                   part_ml: torch.Tensor | None, status: torch.Tensor, one_token_each: bool = False,
-                  tickets: torch.Tensor | None = None) -> None:
+                  tickets: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> None:
     """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores.
     ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys.
     ``tickets`` (decoding; int32, one per sequence and key/value head, zero before the call and after it): with
@@ -386,11 +391,14 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
         raise KernelError("one_token_each needs exactly one token per sequence")
     tickets = tickets if one_token_each else None
     _check_tickets(tickets, sequences, kv_heads)
+    _check_sinks(sinks, heads)
+    if sinks is not None and not one_token_each:
+        raise KernelError("the tensor-core kernel of this file takes sinks only when decoding; prompts with sinks run attention_tcgen05 or attention")
     fn = _fn("attention_mma", "tt_attention_mma", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, heads, kv_heads, head_dim, scale, window, splits, sequences if one_token_each else 0, _ptr(out), _ptr(part_acc),
-              _ptr(part_ml), _ptr(tickets), _ptr(status),
+              _ptr(part_ml), _ptr(tickets), _ptr(status), _ptr(sinks),
               _stream()), "attention_mma", _attention_launches(splits, one_token_each, tickets is not None))
 
 
@@ -449,17 +457,18 @@ def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, he
 
 def attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                       len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
-                      scale: float, window: int, out: torch.Tensor, status: torch.Tensor) -> None:
+                      scale: float, window: int, out: torch.Tensor, status: torch.Tensor, sinks: torch.Tensor | None = None) -> None:
     """Causal attention of packed bfloat16 prompts over the block cache with both products on
-    the tcgen05 tensor cores."""
+    the tcgen05 tensor cores.  ``sinks``: see :func:`attention`."""
+    _check_sinks(sinks, heads)
     if not attention_tcgen05_supports(q.dtype, heads, kv_heads, head_dim):
         raise KernelError(f"the tcgen05 attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
     if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16) or not q.is_contiguous():
         raise KernelError("queries, cache and output must all be contiguous bfloat16")
     fn = _fn("attention_tcgen05", "tt_attention_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                                           c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+                                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
-              n_tokens, heads, kv_heads, head_dim, scale, window, _ptr(out), _ptr(status), _stream()), "attention_tcgen05")
+              n_tokens, heads, kv_heads, head_dim, scale, _ptr(sinks), window, _ptr(out), _ptr(status), _stream()), "attention_tcgen05")
 
 
 # --------------------------------------------------------------------------- recurrent

@@ -145,11 +145,7 @@ class CausalAttention(Mixer):
                                     rot.interleaved, rot.attention_scaling, q, cache.k_pool if cache.writes else None,
                                     cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                                     self.heads, self.kv_heads, self.head_dim, self.value_dim, ctx.status)
-            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
-            part_acc, part_ml = self.slice_scratch(ctx, splits)
-            api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-                          self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
-                          value_dim=self.value_dim, sinks=self.sinks)
+            self.attend(ctx, q, cache, table, mixed)
             return self.out.delta(ctx, mixed, "attention.out")
         if (cache.writes and not ctx.decode and x.dtype == torch.bfloat16
                 and api.gemm_tcgen05_qkv_rope_takes(x, self.qkv.weight, self.head_dim, rot.rotary_dim)):
@@ -221,12 +217,15 @@ class CausalAttention(Mixer):
     def attend(self, ctx, q, cache, table, mixed) -> None:
         """Prompts in bfloat16 with head size 64 or 128: the tcgen05 kernel.  Other bfloat16
         sizes up to 128 and all decoding: the mma.sync kernels.  Everything else (float32,
-        head sizes 48, 80, 144 ...): the exact kernel."""
-        if not ctx.decode and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim):
+        head sizes 48, 80, 144 ..., values of another size than the keys): the exact kernel.
+        Sinks go with the tcgen05 prompt kernel, the mma.sync decode kernel and the exact kernel."""
+        same = self.value_dim == self.head_dim
+        if same and not ctx.decode and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim):
             api.attention_tcgen05(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-                                  self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status)
+                                  self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status, sinks=self.sinks)
             return
-        tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
+        tensor_cores = (same and api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
+                        and (self.sinks is None or ctx.decode))
         if tensor_cores:
             splits = self.decode_slices(ctx)
         else:
@@ -235,7 +234,9 @@ class CausalAttention(Mixer):
         if tensor_cores:
             api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
-                              one_token_each=ctx.decode, tickets=self.tickets(ctx, splits) if ctx.decode else None)
+                              one_token_each=ctx.decode, tickets=self.tickets(ctx, splits) if ctx.decode else None,
+                              sinks=self.sinks if ctx.decode else None)
         else:
             api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-                          self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+                          self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
+                          value_dim=self.value_dim, sinks=self.sinks)
