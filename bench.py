@@ -108,6 +108,64 @@ def reference_arm(config: dict, steps: int, warmup: int) -> int:
     return 0
 
 
+def famalorn_pair(size: str) -> tuple[dict, dict]:
+    """(Famalorn config.json, Llama config.json) of one size: the same width, feed-forward width, vocabulary and number of
+    layers; every Famalorn layer has the feed-forward, and its mixers (gated delta rule, Mamba-2, attention beside
+    Mamba-2, in turn) are sized like published models of their kinds at this width."""
+    width, ff, heads, kv_heads, head_dim, layers = {"1b": (2048, 8192, 32, 8, 64, 6), "3b": (3072, 8192, 24, 8, 128, 6)}[size]
+    llama = dict(SHAPES[SHAPE_NAMES[size]])
+    llama["num_hidden_layers"] = layers
+    mlp = {"kind": "dense", "ff": ff}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": width // 128, "kv_heads": width // 256, "dim": 128, "vdim": 128, "conv": 4}}
+    mamba = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}
+    pair = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                 "rot": {"dims": head_dim // 2, "base": 500000.0}},
+        "right": {"heads": width // 64, "vdim": 64, "state": 64, "groups": 1, "norm_groups": 1, "conv": 4},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    famalorn = {"architecture": "Famalorn", "vocab": llama["vocab_size"], "width": width, "norm": {"eps": 1e-6},
+                "layers": [[delta, mamba, pair][i % 3] for i in range(layers)]}
+    return famalorn, llama
+
+
+def design_bench(args) -> int:
+    """``--design famalorn``: prefill and decode of the Famalorn design beside the Llama decoder at equal size (random
+    weights, bfloat16), with each step's time by class of kernel against that class's bound.  One JSON line."""
+    import thintensor_b200
+    from thintensor_b200.benchmark import class_fractions, measure_classes, measure_decode, measure_prefill
+
+    pk = peaks()
+    import torch
+    out = {"bench": "Famalorn beside Llama at equal width, feed-forward, vocabulary and layers; random weights, bfloat16",
+           "prompt_len": args.prompt_len, "batch": args.batch, "peaks": pk, "sizes": {}}
+    for size in args.sizes.split(","):
+        entry = out["sizes"][size] = {}
+        for name, raw in zip(("famalorn", "llama"), famalorn_pair(size)):
+            runtime = thintensor_b200.random_model(raw, seed=0, dtype="bf16", device="cuda:0")
+            vocab = raw.get("vocab") or raw["vocab_size"]
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist() for _ in range(args.batch)]
+            context = args.prompt_len + args.warmup + args.steps + 64
+            prefill = measure_prefill(runtime, prompts[0], repeats=3, warmup=3)
+            decode = measure_decode(runtime, prompts, context, args.warmup, args.steps)
+            spans = measure_classes(runtime, prompts, context, prefill_prompts=prompts[:1])
+            achieved = decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9
+            entry[name] = {
+                "layers": len(runtime.model.spec.layers),
+                "prefill": {"tokens": prefill["tokens"], "ms": round(prefill["ms"], 3), "tokens_per_s": round(prefill["tokens_per_s"], 1),
+                            "tensor_frac": round(prefill["flops"] / (prefill["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+                "decode": {"batch": args.batch, "ms_per_step": round(decode["ms_per_step"], 4), "tokens_per_s": round(decode["tokens_per_s"], 1),
+                           "bytes_per_step": int(decode["bytes_per_step"]), "hbm_frac": round(achieved / pk["hbm_gbs"], 4),
+                           "launches_per_step": decode["launches_per_step"]},
+                "classes": class_fractions(runtime.model, spans, pk, prompts[:1], args.batch, spans["mean_context"]),
+                "kernels": {step: {k: round(v["ms"], 4) for k, v in list(spans[step].items())[:14]} for step in ("prefill_step", "decode_step")},
+            }
+            del runtime
+            torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -120,7 +178,13 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     parser.add_argument("--shape", choices=sorted(SHAPE_NAMES), default="1b", help="with --only: layer sizes of another model of the family")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
+    parser.add_argument("--design", choices=["famalorn"], help="measure this design beside the Llama decoder at equal size instead of the headline")
+    parser.add_argument("--sizes", default="1b,3b", help="with --design: which sizes (1b: width 2,048; 3b: width 3,072)")
     args = parser.parse_args()
+    if args.design:
+        args.warmup = max(args.warmup, 3)
+        args.steps = min(args.steps, 128)
+        return design_bench(args)
     if args.impl == "reference":
         return reference_arm(dict(SHAPES[SHAPE_NAMES["1b"]]), min(args.steps, 128), args.warmup)
     if args.gpus != 1:

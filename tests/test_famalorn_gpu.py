@@ -287,3 +287,65 @@ def test_a_model_without_attention_keeps_no_keys(folders):
     engine = runtime.new_engine(max_tokens=128, max_sequences=2)
     assert len(engine.cache.kv_groups) == 0 and len(engine.cache.state_groups) > 0
     assert runtime.model.device_driven
+
+
+@pytest.mark.parametrize("name,dtype", [("p", "float32"), ("s", "bfloat16"), ("r", "bfloat16")])
+def test_trace_replay_as_a_subprocess(folders, tmp_path, name, dtype):
+    """``bin/trace_run`` chooses the model class by config.json: prompts of unequal lengths start together, go on one
+    token each, the shorter ones end earlier, and a second batch reuses what the first gave back."""
+    from test_trace_run_gpu import read_step, run_trace
+
+    folder = folders(name, dtype)
+    vocab = CONFIGS[name]["vocab"]
+    requests = {f"q{i}": token_ids(vocab, n, 700 + i) for i, n in enumerate([40, 9, 75, 66])}
+    prompt_len = {"q0": 7, "q1": 1, "q2": 64, "q3": 60}
+    judge = Judge(dtype)
+    steps, expect, n = [], [], 0
+    for batch in (["q0", "q2", "q1"], ["q3"]):
+        at = {k: prompt_len[k] for k in batch}
+        steps.append({"step": n, "entries": [{"id": k, "tokens": requests[k][: at[k]], "want": [0, at[k] - 1]} for k in batch], "end": []})
+        expect.append((n, [(k, place) for k in batch for place in (0, at[k] - 1)]))
+        n += 1
+        live = list(batch)
+        while live:
+            entries, wanted, ending = [], [], []
+            for k in live:
+                entries.append({"id": k, "tokens": [requests[k][at[k]]], "want": [0] if at[k] % 2 else []})
+                if at[k] % 2:
+                    wanted.append((k, at[k]))
+                at[k] += 1
+                if at[k] == len(requests[k]):
+                    ending.append(k)
+            steps.append({"step": n, "entries": entries, "end": ending})
+            expect.append((n, wanted))
+            n += 1
+            live = [k for k in live if k not in ending]
+    run_trace(folder, dtype, tmp_path / "out", 192, steps)
+    for step, wanted in expect:
+        if not wanted:
+            assert not (tmp_path / "out" / f"{step}.f32").exists()
+            continue
+        want = torch.stack([oracle_logits(folder, requests[k])[place] for k, place in wanted])
+        judge.add(read_step(tmp_path / "out", step, vocab), want, f"{name} step {step}")
+    judge.done()
+
+
+def test_command_line(tmp_path):
+    """``random`` writes a model folder from a config.json, ``run`` generates from it greedily, ``bench`` times it."""
+    import json
+
+    import plain_famalorn
+    from test_cli_gpu import cli
+
+    (tmp_path / "config.json").write_text(json.dumps(CONFIGS["p"]))
+    folder = tmp_path / "model"
+    assert cli("random", str(folder), "--config", str(tmp_path / "config.json"), "--seed", "5", "--dtype", "float32").strip() == str(folder)
+    out = json.loads(cli("run", str(folder), "--prompt-token-ids", "5,17,3,100,42", "--max-new-tokens", "5", "--dtype", "fp32",
+                         "--ignore-eos", "--json"))
+    cfg, weights = plain_famalorn.read_model(folder)
+    sequence = [5, 17, 3, 100, 42]
+    for _ in range(5):
+        sequence.append(int(plain_famalorn.forward(cfg, weights, sequence)[-1].argmax()))
+    assert out["generated_token_ids"] == [sequence[5:]]
+    bench = json.loads(cli("bench", str(folder), "--steps", "8", "--warmup", "3", "--prompt-len", "20", "--batch", "2", "--json"))
+    assert bench["tokens_per_s"] > 0 and bench["prefill_tokens_per_s"] > 0

@@ -425,9 +425,10 @@ def test_attention_refuses_bad_sizes():
     from thintensor_b200.kernels import api
 
     with pytest.raises(api.KernelError):
-        api.check_head_dim(24)
+        api.check_head_dim(0)
     with pytest.raises(api.KernelError):
         api.check_head_dim(272)
+    api.check_head_dim(24)          # the exact kernel takes any size up to 256
     assert not api.attention_mma_supports(torch.bfloat16, 4, 2, 48) and not api.attention_mma_supports(torch.float32, 4, 2, 64)
     assert not api.attention_mma_supports(torch.bfloat16, 34, 2, 64) and api.attention_mma_supports(torch.bfloat16, 32, 8, 64)
 

@@ -70,7 +70,7 @@ def kv_bytes_per_token(model) -> int:
     """Bytes of keys and values one cached token takes over all layers."""
     kv, _, source = model.cache_needs()
     width = torch.empty((), dtype=model.dtype).element_size()
-    return sum(2 * need.kv_heads * need.head_dim * width for need, src in zip(kv, source) if need is not None and src is None)
+    return sum(need.kv_heads * (need.head_dim + need.v_dim) * width for need, src in zip(kv, source) if need is not None and src is None)
 
 
 def kv_read_bytes_per_token(model) -> int:
@@ -78,7 +78,21 @@ def kv_read_bytes_per_token(model) -> int:
     them, also one that reads another run's cache."""
     kv, _, _ = model.cache_needs()
     width = torch.empty((), dtype=model.dtype).element_size()
-    return sum(2 * need.kv_heads * need.head_dim * width for need in kv if need is not None)
+    return sum(need.kv_heads * (need.head_dim + need.v_dim) * width for need in kv if need is not None)
+
+
+def state_bytes_per_sequence(model) -> int:
+    """Bytes of fixed-size state (recurrent matrices, carried convolution inputs) one sequence holds over all layers;
+    a decode step reads and writes each of them once."""
+    _, states, _ = model.cache_needs()
+    total = 0
+    for needs in states:
+        for need in needs:
+            count = 1
+            for extent in need.shape:
+                count *= extent
+            total += count * torch.empty((), dtype=need.dtype).element_size()
+    return total
 
 
 def linear_flops_per_token(model) -> int:
@@ -98,7 +112,7 @@ def attention_flops(model, tokens: int) -> float:
     for index, run in enumerate(model.spec.schedule):
         for user, mixer in zip(model.users[index], model.layers[run.layer].mixers()):
             if kv[user] is not None:
-                flops += 2.0 * 2.0 * (tokens * (tokens + 1) / 2) * kv[user].head_dim * getattr(mixer, "heads", kv[user].kv_heads)
+                flops += 2.0 * (tokens * (tokens + 1) / 2) * (kv[user].head_dim + kv[user].v_dim) * getattr(mixer, "heads", kv[user].kv_heads)
     return flops
 
 
@@ -157,10 +171,13 @@ def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[i
     and its attention against it too (the cache it reads); the rest (norms, rotation, embedding,
     sampling) has no bound worth naming and is given as time alone.  Times are those of kernels run
     one after another (see :func:`measure_classes`)."""
+    recurrent = ("tt_mamba2_scan", "tt_delta_scan", "tt_causal_conv", "tt_gated_group_norm")
+
     def split(spans: dict) -> dict:
-        out = {"products": 0.0, "attention": 0.0, "rest": 0.0}
+        out = {"products": 0.0, "attention": 0.0, "recurrence": 0.0, "rest": 0.0}
         for name, entry in spans.items():
-            kind = "products" if name.startswith("tt_gemm") else "attention" if name.startswith("tt_attention") else "rest"
+            kind = ("products" if name.startswith("tt_gemm") else "attention" if name.startswith("tt_attention")
+                    else "recurrence" if name.startswith(recurrent) else "rest")
             out[kind] += entry["ms"]
         return out
 
@@ -173,11 +190,14 @@ def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[i
     return {
         "prefill": {"tokens": tokens, "products_ms": round(prefill["products"], 4), "products_frac": frac(linear, prefill["products"], peak_flops),
                     "attention_ms": round(prefill["attention"], 4), "attention_frac": frac(attention, prefill["attention"], peak_flops),
-                    "rest_ms": round(prefill["rest"], 4)},
+                    "recurrence_ms": round(prefill["recurrence"], 4), "rest_ms": round(prefill["rest"], 4)},
         "decode": {"batch": batch, "products_ms": round(decode["products"], 4),
                    "products_frac": frac(weight_bytes_per_step(model), decode["products"], peak_bytes),
                    "attention_ms": round(decode["attention"], 4),
                    "attention_frac": frac(kv_read_bytes_per_token(model) * mean_context * batch, decode["attention"], peak_bytes),
+                   # recurrences (convolution, state update, gated norm): every state read and written once
+                   "recurrence_ms": round(decode["recurrence"], 4),
+                   "recurrence_frac": frac(2 * state_bytes_per_sequence(model) * batch, decode["recurrence"], peak_bytes),
                    "rest_ms": round(decode["rest"], 4)},
         "how": "CUDA events around every kernel, kernels run one after another (no overlap between them)",
     }
@@ -247,7 +267,8 @@ def measure_decode(runtime, prompts: list[list[int]], context: int, warmup: int,
     engine.check_status()
     ms = start.elapsed_time(stop)
     mean_context = sum(lengths_before) / batch + (steps - 1) / 2.0
-    bytes_per_step = weight_bytes_per_step(runtime.model) + kv_read_bytes_per_token(runtime.model) * mean_context * batch
+    bytes_per_step = (weight_bytes_per_step(runtime.model) + kv_read_bytes_per_token(runtime.model) * mean_context * batch
+                      + 2 * state_bytes_per_sequence(runtime.model) * batch)
     result = {
         "ms_per_step": ms / steps,
         "tokens_per_s": batch * steps / (ms / 1e3),

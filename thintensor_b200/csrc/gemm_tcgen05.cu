@@ -94,8 +94,16 @@ struct Args {
     QkvRope rope;            // qkv form only
     int rope_head_dim;       // 64 or 128
     int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
+    int activation;          // SWIGLU forms: what the gate passes through: 0 silu, 1 relu, 2 the tanh form of gelu
     unsigned* status;
 };
+
+// the gate's activation of the gated forms: act(gate) * up is what they store
+__device__ __forceinline__ float gate_activation(float g, int activation) {
+    if (activation == 1) return fmaxf(g, 0.0f);
+    if (activation == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return __fdividef(g, 1.0f + __expf(-g));
+}
 
 // GROUP: k-blocks that share one round of the full / empty barriers (STAGES is a multiple of it).  With few tokens
 // a k-block is four short products; waiting, fencing and committing once per k-block cost the issuing thread more
@@ -258,7 +266,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 16; ++j) {
                             const int token = b_row + c + j;
                             if (token < args.tokens)
-                                out[(size_t)token * args.ld_out + feature] = __float2bfloat16_rn(g[j] / (1.0f + __expf(-g[j])) * exchange[r * PITCH + c + j]);
+                                out[(size_t)token * args.ld_out + feature] = __float2bfloat16_rn(gate_activation(g[j], args.activation) * exchange[r * PITCH + c + j]);
                         }
                     }
                 }
@@ -295,7 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int f = f0 + j;
-                            if (f < args.features) out[f] = __float2bfloat16_rn(g[j] / (1.0f + __expf(-g[j])) * u[j]);
+                            if (f < args.features) out[f] = __float2bfloat16_rn(gate_activation(g[j], args.activation) * u[j]);
                         }
                     }
                 }
@@ -368,7 +376,7 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
-                        y[e] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        y[e] = gate_activation(g, args.activation) * u;
                     }
                     if (vec && f + 8 <= args.features) {
                         const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
@@ -505,7 +513,7 @@ __device__ __forceinline__ void store_swiglu_bulk(uint32_t lane_addr, int first_
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
-                y[e] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                y[e] = gate_activation(g, args.activation) * u;
             }
             const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
             const __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
@@ -1278,7 +1286,11 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
         return (int)cudaErrorInvalidValue;
     const int k_blocks = (k + BK - 1) / BK;
     if (splits > k_blocks) splits = k_blocks;
+    const int activation = form >> 4;       // the gated form carries its gate's activation in the bits above the form
+    form &= 15;
+    if (activation < 0 || activation > 2 || (activation && form != 1)) return (int)cudaErrorInvalidValue;
     Args args;
+    args.activation = activation;
     args.bias = bias; args.out = out; args.ld_out = ld_out; args.split_stride = split_stride;
     args.tokens = tokens; args.features = features; args.k = k;
     args.k_blocks_per_split = (k_blocks + splits - 1) / splits;

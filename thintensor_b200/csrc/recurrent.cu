@@ -23,10 +23,45 @@ constexpr int REC_CHUNK = 16;       // tokens staged in shared memory at a time
 constexpr int REC_MAX_ROWS = 256;   // largest state size per column (N of Mamba-2, key size of the delta rule)
 constexpr int CONV_MAX_TAPS = 8;
 
+// sum of one element over the k-slices of a projection: four loads in flight together, additions in slice order
 __device__ __forceinline__ float rec_sum_slices(const float* __restrict__ p, int splits, size_t split_stride) {
     float total = 0.0f;
-    for (int s = 0; s < splits; ++s) total += __ldg(p + (size_t)s * split_stride);
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+        const float a = __ldg(p + (size_t)s * split_stride), b = __ldg(p + (size_t)(s + 1) * split_stride);
+        const float c = __ldg(p + (size_t)(s + 2) * split_stride), d = __ldg(p + (size_t)(s + 3) * split_stride);
+        total = (((total + a) + b) + c) + d;
+    }
+    for (; s < splits; ++s) total += __ldg(p + (size_t)s * split_stride);
     return total;
+}
+
+// Asynchronous copies into shared memory: a chunk of tokens is fetched while the chunk before it is worked on.
+__device__ __forceinline__ uint32_t rec_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void rec_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(rec_smem(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rec_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(rec_smem(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rec_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void rec_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// rows x width floats from src (row stride src_stride) to dst (row stride dst_stride), all threads of the block taking
+// part; vec: every row start and the width are multiples of four floats and both bases are 16-byte aligned
+__device__ __forceinline__ void rec_stage(float* dst, int dst_stride, const float* src, size_t src_stride, int rows, int width, bool vec) {
+    if (vec) {
+        const int quads = width >> 2;
+        for (int e = threadIdx.x; e < rows * quads; e += blockDim.x) {
+            const int k = e / quads, r = (e - k * quads) << 2;
+            rec_copy16(dst + k * dst_stride + r, src + (size_t)k * src_stride + r);
+        }
+    } else {
+        for (int e = threadIdx.x; e < rows * width; e += blockDim.x) {
+            const int k = e / width, r = e - k * width;
+            rec_copy4(dst + k * dst_stride + r, src + (size_t)k * src_stride + r);
+        }
+    }
 }
 
 __device__ __forceinline__ float rec_silu(float x) { return x / (1.0f + expf(-x)); }
@@ -137,15 +172,13 @@ __global__ void __launch_bounds__(REC_COLS* REC_LANES)
 mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __restrict__ proj, int splits, size_t split_stride,
                    int cols, int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                    const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
-                   const int* __restrict__ cu, const int* __restrict__ slots, int heads, int P, int N, int groups) {
+                   const int* __restrict__ cu, const int* __restrict__ slots, int heads, int P, int N, int groups, int chunk,
+                   int vec) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float rec_shared[];
-    float* Bs = rec_shared;                          // [REC_CHUNK][N]
-    float* Cs = Bs + REC_CHUNK * N;                  // [REC_CHUNK][N]
-    float* xs = Cs + REC_CHUNK * N;                  // [REC_CHUNK][REC_COLS]
-    float* decay = xs + REC_CHUNK * REC_COLS;        // [REC_CHUNK]
-    float* step = decay + REC_CHUNK;                 // [REC_CHUNK]
+    extern __shared__ __align__(16) float rec_shared[];
+    // two buffers of: B [chunk][N], C [chunk][N], x [chunk][REC_COLS], decay [chunk], step [chunk]
+    const int buffer_floats = 2 * chunk * N + chunk * REC_COLS + 2 * chunk;
     const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
@@ -154,6 +187,28 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     const int lane = threadIdx.x % REC_LANES, col = threadIdx.x / REC_LANES;
     const int p = p0 + col;
     const bool live = p < P;
+    const int width = min(REC_COLS, P - p0);                    // columns of this tile that exist
+    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), skip = __ldg(d_skip + h);
+    const bool vec_x = vec && (width & 3) == 0;
+
+    auto stage = [&](int c0, float* base) {                      // asynchronous: B, C and x of tokens c0 .. of this sequence
+        const int count = min(chunk, n - c0);
+        const float* row = xbc + (size_t)(first + c0) * xbc_cols;
+        rec_stage(base, N, row + inner + g * N, xbc_cols, count, N, vec);
+        rec_stage(base + chunk * N, N, row + inner + groups * N + g * N, xbc_cols, count, N, vec);
+        rec_stage(base + 2 * chunk * N, REC_COLS, row + h * P + p0, xbc_cols, count, width, vec_x);
+        rec_commit();
+    };
+    auto raw_step = [&](int c0) {                                // this thread's token of the chunk: the raw step size
+        return rec_sum_slices(proj + (size_t)(first + c0 + threadIdx.x) * cols + dt_col + h, splits, split_stride);
+    };
+    auto put_scalars = [&](float* base, float raw) {
+        const float dt = rec_softplus(raw + bias);
+        base[2 * chunk * N + chunk * REC_COLS + threadIdx.x] = expf(neg_a * dt);
+        base[2 * chunk * N + chunk * REC_COLS + chunk + threadIdx.x] = dt;
+    };
+
+    stage(0, rec_shared);
     float* S = state + (((size_t)slots[b] * heads + h) * P + (live ? p : 0)) * N;
     float s[K];
 #pragma unroll
@@ -161,44 +216,50 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         const int r = lane + i * REC_LANES;
         s[i] = (live && r < N) ? S[r] : 0.0f;
     }
-    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), skip = __ldg(d_skip + h);
-    for (int c0 = 0; c0 < n; c0 += REC_CHUNK) {
-        const int count = min(REC_CHUNK, n - c0);
-        __syncthreads();                             // the chunk before is done with
-        for (int e = threadIdx.x; e < count * N; e += blockDim.x) {
-            const int k = e / N, r = e - k * N;
-            const float* row = xbc + (size_t)(first + c0 + k) * xbc_cols;
-            Bs[k * N + r] = row[inner + g * N + r];
-            Cs[k * N + r] = row[inner + groups * N + g * N + r];
-        }
-        for (int e = threadIdx.x; e < count * REC_COLS; e += blockDim.x) {
-            const int k = e / REC_COLS, q = e - k * REC_COLS;
-            xs[e] = (p0 + q < P) ? xbc[(size_t)(first + c0 + k) * xbc_cols + h * P + p0 + q] : 0.0f;
-        }
-        if (threadIdx.x < count) {
-            const float raw = rec_sum_slices(proj + (size_t)(first + c0 + threadIdx.x) * cols + dt_col + h, splits, split_stride);
-            const float dt = rec_softplus(raw + bias);
-            step[threadIdx.x] = dt;
-            decay[threadIdx.x] = expf(neg_a * dt);
+    if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_step(0));
+    int it = 0;
+    for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
+        float* cur = rec_shared + (it & 1) * buffer_floats;
+        float* nxt = rec_shared + ((it + 1) & 1) * buffer_floats;
+        const int count = min(chunk, n - c0);
+        const int count_next = min(chunk, n - c0 - chunk);       // <= 0: this is the last chunk
+        float raw_next = 0.0f;
+        if (count_next > 0) {
+            stage(c0 + chunk, nxt);                              // lands while this chunk is worked on
+            if (threadIdx.x < count_next) raw_next = raw_step(c0 + chunk);
+            rec_wait<1>();
+        } else {
+            rec_wait<0>();
         }
         __syncthreads();
+        const float* Bs = cur;
+        const float* Cs = cur + chunk * N;
+        const float* xs = cur + 2 * chunk * N;
+        const float* decay = xs + chunk * REC_COLS;
+        const float* step = decay + chunk;
         for (int k = 0; k < count; ++k) {
-            const float a = decay[k], x = xs[k * REC_COLS + col];
+            const float a = decay[k], x = live ? xs[k * REC_COLS + col] : 0.0f;
             const float dx = step[k] * x;
             const float* Bk = Bs + k * N;
             const float* Ck = Cs + k * N;
-            float part = 0.0f;
+            float part0 = 0.0f, part1 = 0.0f;                    // two chains, so that neighbouring rows do not wait for each other
 #pragma unroll
-            for (int i = 0; i < K; ++i) {
-                const int r = lane + i * REC_LANES;
-                if (r < N) {
-                    s[i] = fmaf(dx, Bk[r], a * s[i]);
-                    part = fmaf(s[i], Ck[r], part);
+            for (int i = 0; i < K; i += 2) {
+                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
+                if (r0 < N) {
+                    s[i] = fmaf(dx, Bk[r0], a * s[i]);
+                    part0 = fmaf(s[i], Ck[r0], part0);
+                }
+                if (r1 < N) {
+                    s[i + 1] = fmaf(dx, Bk[r1], a * s[i + 1]);
+                    part1 = fmaf(s[i + 1], Ck[r1], part1);
                 }
             }
-            part = rec_group_sum(part);
+            const float part = rec_group_sum(part0 + part1);
             if (lane == 0 && live) y[(size_t)(first + c0 + k) * inner + h * P + p] = fmaf(skip, x, part);
         }
+        if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
+        __syncthreads();                                         // this buffer may be filled again; the next one's scalars are written
     }
     if (live) {
 #pragma unroll
@@ -209,6 +270,11 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     }
 }
 
+// Tokens staged at a time: 16 where two buffers of them fit the default 48 KB of shared memory, else 8.
+static int rec_chunk(int rows) { return rows <= 128 ? REC_CHUNK : REC_CHUNK / 2; }
+static size_t rec_shared_bytes(int rows, int chunk) { return (size_t)2 * (2 * chunk * rows + chunk * REC_COLS + 2 * chunk) * sizeof(float); }
+static bool rec_aligned(const void* p, int a, int b, int c, int d) { return (((uintptr_t)p & 15) == 0) && !((a | b | c | d) & 3); }
+
 extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
                               int dt_col, const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
                               const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups,
@@ -216,8 +282,10 @@ extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj,
     if (sequences <= 0) return 0;
     if (N <= 0 || N > REC_MAX_ROWS || P <= 0 || groups <= 0 || heads % groups || sequences > 65535) return (int)cudaErrorInvalidValue;
     const dim3 grid(heads, sequences, (P + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
-    const size_t shared = (size_t)(2 * REC_CHUNK * N + REC_CHUNK * REC_COLS + 2 * REC_CHUNK) * sizeof(float);
-#define TT_SCAN(K) tt_launch_pdl(mamba2_scan_kernel<K>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups)
+    const int chunk = rec_chunk(N);
+    const size_t shared = rec_shared_bytes(N, chunk);
+    const int vec = rec_aligned(xbc, xbc_cols, N, P, 0) ? 1 : 0;          // every row piece starts on 16 bytes
+#define TT_SCAN(K) tt_launch_pdl(mamba2_scan_kernel<K>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups, chunk, vec)
     if (N <= 8 * REC_LANES) TT_SCAN(8);
     else if (N <= 16 * REC_LANES) TT_SCAN(16);
     else TT_SCAN(32);
@@ -238,15 +306,12 @@ __global__ void __launch_bounds__(REC_COLS* REC_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __restrict__ proj, int splits, size_t split_stride,
                   int cols, int b_col, int a_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                   float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slots,
-                  int heads, int qk_heads, int D, int V) {
+                  int heads, int qk_heads, int D, int V, int chunk, int vec) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float rec_shared[];
-    float* qs = rec_shared;                          // [REC_CHUNK][D]
-    float* ks = qs + REC_CHUNK * D;                  // [REC_CHUNK][D]
-    float* vs = ks + REC_CHUNK * D;                  // [REC_CHUNK][REC_COLS]
-    float* decay = vs + REC_CHUNK * REC_COLS;        // [REC_CHUNK]
-    float* beta = decay + REC_CHUNK;                 // [REC_CHUNK]
+    extern __shared__ __align__(16) float rec_shared[];
+    // two buffers of: q [chunk][D], k [chunk][D], v [chunk][REC_COLS], decay [chunk], beta [chunk]
+    const int buffer_floats = 2 * chunk * D + chunk * REC_COLS + 2 * chunk;
     const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
@@ -255,6 +320,29 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
     const int warp = threadIdx.x >> 5, wlane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int p = p0 + col;
     const bool live = p < V;
+    const int width = min(REC_COLS, V - p0);
+    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), q_scale = rsqrtf((float)D);
+    const int k_off = qk_heads * D, v_off = 2 * qk_heads * D;
+    const bool vec_v = vec && (width & 3) == 0;
+
+    auto stage = [&](int c0, float* base) {
+        const int count = min(chunk, n - c0);
+        const float* row = qkv + (size_t)(first + c0) * qkv_cols;
+        rec_stage(base, D, row + g * D, qkv_cols, count, D, vec);
+        rec_stage(base + chunk * D, D, row + k_off + g * D, qkv_cols, count, D, vec);
+        rec_stage(base + 2 * chunk * D, REC_COLS, row + v_off + h * V + p0, qkv_cols, count, width, vec_v);
+        rec_commit();
+    };
+    auto raw_pair = [&](int c0) {                                // this thread's token of the chunk: raw write strength, raw decay input
+        const float* row = proj + (size_t)(first + c0 + threadIdx.x) * cols;
+        return make_float2(rec_sum_slices(row + b_col + h, splits, split_stride), rec_sum_slices(row + a_col + h, splits, split_stride));
+    };
+    auto put_scalars = [&](float* base, float2 raw) {
+        base[2 * chunk * D + chunk * REC_COLS + threadIdx.x] = expf(neg_a * rec_softplus(raw.y + bias));
+        base[2 * chunk * D + chunk * REC_COLS + chunk + threadIdx.x] = 1.0f / (1.0f + expf(-raw.x));
+    };
+
+    stage(0, rec_shared);
     float* S = state + (((size_t)slots[b] * heads + h) * V + (live ? p : 0)) * D;
     float s[K];
 #pragma unroll
@@ -262,64 +350,60 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         const int r = lane + i * REC_LANES;
         s[i] = (live && r < D) ? S[r] : 0.0f;
     }
-    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), q_scale = rsqrtf((float)D);
-    const int k_off = qk_heads * D, v_off = 2 * qk_heads * D;
-    for (int c0 = 0; c0 < n; c0 += REC_CHUNK) {
-        const int count = min(REC_CHUNK, n - c0);
+    if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_pair(0));
+    int it = 0;
+    for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
+        float* cur = rec_shared + (it & 1) * buffer_floats;
+        float* nxt = rec_shared + ((it + 1) & 1) * buffer_floats;
+        const int count = min(chunk, n - c0);
+        const int count_next = min(chunk, n - c0 - chunk);
+        float2 raw_next = make_float2(0.0f, 0.0f);
+        if (count_next > 0) {
+            stage(c0 + chunk, nxt);
+            if (threadIdx.x < count_next) raw_next = raw_pair(c0 + chunk);
+            rec_wait<1>();
+        } else {
+            rec_wait<0>();
+        }
         __syncthreads();
-        // a warp per (token, q or k): load, sum of squares, scale to unit length
+        float* qs = cur;
+        float* ks = cur + chunk * D;
+        // a warp per (token, q or k): sum of squares, scale to unit length (q also by D^-1/2)
         for (int item = warp; item < 2 * count; item += warps) {
-            const int k = item >> 1, is_k = item & 1;
-            const float* src = qkv + (size_t)(first + c0 + k) * qkv_cols + (is_k ? k_off : 0) + g * D;
-            float* dst = (is_k ? ks : qs) + k * D;
+            float* vecp = (item & 1 ? ks : qs) + (item >> 1) * D;
             float sumsq = 0.0f;
-            for (int r = wlane; r < D; r += 32) {
-                const float v = src[r];
-                dst[r] = v;
-                sumsq += v * v;
-            }
-            const float scale = rsqrtf(tt_warp_sum(sumsq) + 1e-6f) * (is_k ? 1.0f : q_scale);
-            __syncwarp();
-            for (int r = wlane; r < D; r += 32) dst[r] *= scale;
-        }
-        for (int e = threadIdx.x; e < count * REC_COLS; e += blockDim.x) {
-            const int k = e / REC_COLS, q = e - k * REC_COLS;
-            vs[e] = (p0 + q < V) ? qkv[(size_t)(first + c0 + k) * qkv_cols + v_off + h * V + p0 + q] : 0.0f;
-        }
-        if (threadIdx.x < count) {
-            const float* row = proj + (size_t)(first + c0 + threadIdx.x) * cols;
-            const float braw = rec_sum_slices(row + b_col + h, splits, split_stride);
-            const float araw = rec_sum_slices(row + a_col + h, splits, split_stride);
-            beta[threadIdx.x] = 1.0f / (1.0f + expf(-braw));
-            decay[threadIdx.x] = expf(neg_a * rec_softplus(araw + bias));
+            for (int r = wlane; r < D; r += 32) sumsq = fmaf(vecp[r], vecp[r], sumsq);
+            const float scale = rsqrtf(tt_warp_sum(sumsq) + 1e-6f) * (item & 1 ? 1.0f : q_scale);
+            for (int r = wlane; r < D; r += 32) vecp[r] *= scale;
         }
         __syncthreads();
+        const float* vs = cur + 2 * chunk * D;
+        const float* decay = vs + chunk * REC_COLS;
+        const float* beta = decay + chunk;
         for (int k = 0; k < count; ++k) {
             const float a = decay[k];
             const float* qk = qs + k * D;
             const float* kk = ks + k * D;
-            float part = 0.0f;
+            float part0 = 0.0f, part1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < K; ++i) {
-                const int r = lane + i * REC_LANES;
-                if (r < D) {
-                    s[i] *= a;
-                    part = fmaf(s[i], kk[r], part);
-                }
+            for (int i = 0; i < K; i += 2) {
+                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
+                if (r0 < D) { s[i] *= a; part0 = fmaf(s[i], kk[r0], part0); }
+                if (r1 < D) { s[i + 1] *= a; part1 = fmaf(s[i + 1], kk[r1], part1); }
             }
-            const float u = beta[k] * (vs[k * REC_COLS + col] - rec_group_sum(part));
-            part = 0.0f;
+            const float u = beta[k] * ((live ? vs[k * REC_COLS + col] : 0.0f) - rec_group_sum(part0 + part1));
+            part0 = 0.0f, part1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < K; ++i) {
-                const int r = lane + i * REC_LANES;
-                if (r < D) {
-                    s[i] = fmaf(kk[r], u, s[i]);
-                    part = fmaf(s[i], qk[r], part);
-                }
+            for (int i = 0; i < K; i += 2) {
+                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
+                if (r0 < D) { s[i] = fmaf(kk[r0], u, s[i]); part0 = fmaf(s[i], qk[r0], part0); }
+                if (r1 < D) { s[i + 1] = fmaf(kk[r1], u, s[i + 1]); part1 = fmaf(s[i + 1], qk[r1], part1); }
             }
-            part = rec_group_sum(part);
+            const float part = rec_group_sum(part0 + part1);
             if (lane == 0 && live) o[(size_t)(first + c0 + k) * (heads * V) + h * V + p] = part;
         }
+        if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
@@ -337,8 +421,10 @@ extern "C" int tt_delta_scan(const float* qkv, int qkv_cols, const float* proj, 
     if (sequences <= 0) return 0;
     if (D <= 0 || D > REC_MAX_ROWS || V <= 0 || qk_heads <= 0 || heads % qk_heads || sequences > 65535) return (int)cudaErrorInvalidValue;
     const dim3 grid(heads, sequences, (V + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
-    const size_t shared = (size_t)(2 * REC_CHUNK * D + REC_CHUNK * REC_COLS + 2 * REC_CHUNK) * sizeof(float);
-#define TT_SCAN(K) tt_launch_pdl(delta_scan_kernel<K>, grid, block, shared, stream, qkv, qkv_cols, proj, splits, (size_t)split_stride, cols, b_col, a_col, dt_bias, a_log, state, o, cu, slots, heads, qk_heads, D, V)
+    const int chunk = rec_chunk(D);
+    const size_t shared = rec_shared_bytes(D, chunk);
+    const int vec = rec_aligned(qkv, qkv_cols, D, V, 0) ? 1 : 0;
+#define TT_SCAN(K) tt_launch_pdl(delta_scan_kernel<K>, grid, block, shared, stream, qkv, qkv_cols, proj, splits, (size_t)split_stride, cols, b_col, a_col, dt_bias, a_log, state, o, cu, slots, heads, qk_heads, D, V, chunk, vec)
     if (D <= 8 * REC_LANES) TT_SCAN(8);
     else if (D <= 16 * REC_LANES) TT_SCAN(16);
     else TT_SCAN(32);
@@ -382,6 +468,47 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int width, 
     }
 }
 
+// The same with a group's numbers kept in registers between the two passes (up to GN_VALUES per thread), so every
+// input is loaded once and all loads of a thread are in flight together: the form for groups of up to 8,192 numbers.
+constexpr int GN_VALUES = 8;
+
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+gated_group_norm_reg_kernel(const float* __restrict__ y, int width, int group, const float* __restrict__ proj, int splits,
+                            size_t split_stride, int cols, int gate_col, const float* __restrict__ weight, int weight_len,
+                            float eps, int gate_first, TOut* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    __shared__ float reduce[32];
+    const int groups = width / group;
+    const int t = blockIdx.x / groups, gi = blockIdx.x - t * groups;
+    const float* yr = y + (size_t)t * width + (size_t)gi * group;
+    const float* gr = proj + (size_t)t * cols + gate_col + (size_t)gi * group;
+    float v[GN_VALUES], gate[GN_VALUES];
+    float sumsq = 0.0f;
+#pragma unroll
+    for (int e = 0; e < GN_VALUES; ++e) {
+        const int j = threadIdx.x + e * blockDim.x;
+        v[e] = 0.0f;
+        gate[e] = 0.0f;
+        if (j < group) {
+            gate[e] = rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+            v[e] = gate_first ? yr[j] * gate[e] : yr[j];
+            sumsq = fmaf(v[e], v[e], sumsq);
+        }
+    }
+    const float r = rsqrtf(tt_block_sum(sumsq, reduce) / (float)group + eps);
+    TOut* o = out + (size_t)t * width + (size_t)gi * group;
+#pragma unroll
+    for (int e = 0; e < GN_VALUES; ++e) {
+        const int j = threadIdx.x + e * blockDim.x;
+        if (j < group) {
+            const float w = __ldg(weight + (gi * group + j) % weight_len);
+            o[j] = tt_from_float<TOut>(gate_first ? v[e] * r * w : v[e] * r * w * gate[e]);
+        }
+    }
+}
+
 extern "C" int tt_gated_group_norm(const float* y, int n_tokens, int width, int group, const float* proj, int splits,
                                    long long split_stride, int cols, int gate_col, const float* weight, int weight_len, float eps,
                                    int gate_first, void* out, int out_dtype, cudaStream_t stream) {
@@ -389,6 +516,15 @@ extern "C" int tt_gated_group_norm(const float* y, int n_tokens, int width, int 
     if (group <= 0 || width % group || weight_len <= 0) return (int)cudaErrorInvalidValue;
     const long long blocks = (long long)n_tokens * (width / group);
     if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
+    if (group <= 1024 * GN_VALUES) {
+        int threads = (((group + 3) / 4 + 31) / 32) * 32;       // about four numbers a thread
+        if (threads > 1024) threads = 1024;
+        if (out_dtype == TT_F32)
+            tt_launch_pdl(gated_group_norm_reg_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out);
+        else
+            tt_launch_pdl(gated_group_norm_reg_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out);
+        TT_LAUNCH_CHECK();
+    }
     const int threads = group >= 2048 ? 256 : (group >= 256 ? 128 : (group > 32 ? 64 : 32));
     if (out_dtype == TT_F32)
         tt_launch_pdl(gated_group_norm_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out);

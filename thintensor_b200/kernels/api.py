@@ -803,16 +803,18 @@ def gemm_tcgen05_failure_drill(wait_limit_ns: int, undelivered_bytes: int) -> No
     lib.tt_gemm_tcgen05_expect_undelivered_bytes(int(undelivered_bytes))
 
 
-def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor) -> None:
-    """act = silu(x @ gate.T) * (x @ up.T) in bfloat16, where ``w`` [2 * inter, k] holds
-    the gate rows followed by the up rows; the activation never exists in float32 in
+def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor, activation: str = "silu") -> None:
+    """act = f(x @ gate.T) * (x @ up.T) in bfloat16, where ``w`` [2 * inter, k] holds
+    the gate rows followed by the up rows and f is silu, relu or gelu_tanh; the activation never exists in float32 in
     global memory."""
     _need(act, torch.bfloat16, "activation output")
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"gate activation {activation!r} is not one of {sorted(GATE_ACTIVATIONS)}")
     tokens, k = x.shape
     inter = w.shape[0] // 2
     if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(act.shape) != (tokens, inter):
         raise KernelError(f"tcgen05 swiglu gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / act {tuple(act.shape)}")
     fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
                                                  c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong])
-    _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(None), _ptr(act), act.stride(0), 0, tokens, inter, k, 1, 1,
-              _ptr(status), _stream(), _ptr(None), 0), "gemm_tcgen05_swiglu")
+    _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(None), _ptr(act), act.stride(0), 0, tokens, inter, k, 1,
+              1 + 16 * GATE_ACTIVATIONS[activation], _ptr(status), _stream(), _ptr(None), 0), "gemm_tcgen05_swiglu")
