@@ -11,13 +11,15 @@
 // same chain of operations and give the same bits.
 //
 // A state matrix is owned column by column: the column of value dimension p (all its N state rows)
-// belongs to a group of REC_LANES neighbouring lanes, lane l holding rows l, l + REC_LANES, ... in
-// registers.  Row products with the token's vectors (read from shared memory, where a chunk of tokens
+// belongs to a group of REC_LANES neighbouring lanes, lane l holding rows 4l .. 4l + 3, 4l + 32 .. 4l + 35, ...
+// in registers (four neighbouring rows at a time, so that a token's vectors come out of shared memory, and the
+// state out of global memory, in 16-byte pieces that the group's lanes read side by side).  Row products with the token's vectors (read from shared memory, where a chunk of tokens
 // is staged) are summed inside the group with shuffles.  Columns are independent, so a CTA takes
 // REC_COLS of them for one (sequence, head) and the grid is heads x sequences x column tiles.
 #include "common.cuh"
 
-constexpr int REC_LANES = 8;        // lanes that share one state column
+constexpr int REC_LANES = 8;        // lanes that share one state column (measured on a B200, 64 heads of 64 x 128: one sequence of 2,048
+                                    // tokens 0.79 ms with 8 lanes and 0.86 ms with 16; one token of 64 sequences 70 us and 94 us)
 constexpr int REC_COLS = 32;        // state columns of a CTA (REC_COLS * REC_LANES threads)
 constexpr int REC_CHUNK = 16;       // tokens staged in shared memory at a time
 constexpr int REC_MAX_ROWS = 256;   // largest state size per column (N of Mamba-2, key size of the delta rule)
@@ -66,6 +68,50 @@ __device__ __forceinline__ void rec_stage(float* dst, int dst_stride, const floa
 
 __device__ __forceinline__ float rec_silu(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float rec_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// the state row that register i of lane `lane` holds
+__device__ __forceinline__ int rec_row(int lane, int i) { return 4 * lane + 4 * REC_LANES * (i >> 2) + (i & 3); }
+
+// a column's registers from / to its N numbers in global memory
+template <int K>
+__device__ __forceinline__ void rec_load_column(float (&s)[K], const float* __restrict__ S, int lane, int N, bool live) {
+#pragma unroll
+    for (int j = 0; j < K / 4; ++j) {
+        const int r = rec_row(lane, 4 * j);
+        if (live && !(N & 3) && r < N) {
+            const float4 v = *reinterpret_cast<const float4*>(S + r);
+            s[4 * j] = v.x; s[4 * j + 1] = v.y; s[4 * j + 2] = v.z; s[4 * j + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[4 * j + e] = (live && r + e < N) ? S[r + e] : 0.0f;
+        }
+    }
+}
+template <int K>
+__device__ __forceinline__ void rec_store_column(const float (&s)[K], float* __restrict__ S, int lane, int N) {
+#pragma unroll
+    for (int j = 0; j < K / 4; ++j) {
+        const int r = rec_row(lane, 4 * j);
+        if (!(N & 3) && r < N) {
+            *reinterpret_cast<float4*>(S + r) = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (r + e < N) S[r + e] = s[4 * j + e];
+        }
+    }
+}
+
+// a token's vector (K * REC_LANES numbers in shared memory, zero beyond the real ones) into the registers that match the column's
+template <int K>
+__device__ __forceinline__ void rec_load_vector(float (&v)[K], const float* __restrict__ row, int lane) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll
+    for (int j = 0; j < K / 4; ++j) {
+        const float4 q = row4[lane + REC_LANES * j];
+        v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+    }
+}
 
 __device__ __forceinline__ float rec_group_sum(float v) {
 #pragma unroll
@@ -177,8 +223,10 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ __align__(16) float rec_shared[];
-    // two buffers of: B [chunk][N], C [chunk][N], x [chunk][REC_COLS], decay [chunk], step [chunk]
-    const int buffer_floats = 2 * chunk * N + chunk * REC_COLS + 2 * chunk;
+    // two buffers of: B [chunk][NP], C [chunk][NP], x [chunk][REC_COLS], decay [chunk], step [chunk]; rows are padded to
+    // NP = K * REC_LANES numbers and the padding is zero, so the token loop needs no bounds
+    constexpr int NP = K * REC_LANES;
+    const int buffer_floats = 2 * chunk * NP + chunk * REC_COLS + 2 * chunk;
     const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
@@ -194,9 +242,9 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     auto stage = [&](int c0, float* base) {                      // asynchronous: B, C and x of tokens c0 .. of this sequence
         const int count = min(chunk, n - c0);
         const float* row = xbc + (size_t)(first + c0) * xbc_cols;
-        rec_stage(base, N, row + inner + g * N, xbc_cols, count, N, vec);
-        rec_stage(base + chunk * N, N, row + inner + groups * N + g * N, xbc_cols, count, N, vec);
-        rec_stage(base + 2 * chunk * N, REC_COLS, row + h * P + p0, xbc_cols, count, width, vec_x);
+        rec_stage(base, NP, row + inner + g * N, xbc_cols, count, N, vec);
+        rec_stage(base + chunk * NP, NP, row + inner + groups * N + g * N, xbc_cols, count, N, vec);
+        rec_stage(base + 2 * chunk * NP, REC_COLS, row + h * P + p0, xbc_cols, count, width, vec_x);
         rec_commit();
     };
     auto raw_step = [&](int c0) {                                // this thread's token of the chunk: the raw step size
@@ -204,18 +252,16 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     };
     auto put_scalars = [&](float* base, float raw) {
         const float dt = rec_softplus(raw + bias);
-        base[2 * chunk * N + chunk * REC_COLS + threadIdx.x] = expf(neg_a * dt);
-        base[2 * chunk * N + chunk * REC_COLS + chunk + threadIdx.x] = dt;
+        base[2 * chunk * NP + chunk * REC_COLS + threadIdx.x] = expf(neg_a * dt);
+        base[2 * chunk * NP + chunk * REC_COLS + chunk + threadIdx.x] = dt;
     };
 
+    for (int e = threadIdx.x; e < 2 * buffer_floats; e += blockDim.x) rec_shared[e] = 0.0f;
+    __syncthreads();
     stage(0, rec_shared);
     float* S = state + (((size_t)slots[b] * heads + h) * P + (live ? p : 0)) * N;
     float s[K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) {
-        const int r = lane + i * REC_LANES;
-        s[i] = (live && r < N) ? S[r] : 0.0f;
-    }
+    rec_load_column<K>(s, S, lane, N, live);
     if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_step(0));
     int it = 0;
     for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
@@ -233,27 +279,23 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         }
         __syncthreads();
         const float* Bs = cur;
-        const float* Cs = cur + chunk * N;
-        const float* xs = cur + 2 * chunk * N;
+        const float* Cs = cur + chunk * NP;
+        const float* xs = cur + 2 * chunk * NP;
         const float* decay = xs + chunk * REC_COLS;
         const float* step = decay + chunk;
         for (int k = 0; k < count; ++k) {
             const float a = decay[k], x = live ? xs[k * REC_COLS + col] : 0.0f;
             const float dx = step[k] * x;
-            const float* Bk = Bs + k * N;
-            const float* Ck = Cs + k * N;
+            float bv[K], cv[K];                                  // all of the token's loads are asked for before the arithmetic
+            rec_load_vector<K>(bv, Bs + k * NP, lane);
+            rec_load_vector<K>(cv, Cs + k * NP, lane);
             float part0 = 0.0f, part1 = 0.0f;                    // two chains, so that neighbouring rows do not wait for each other
 #pragma unroll
             for (int i = 0; i < K; i += 2) {
-                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
-                if (r0 < N) {
-                    s[i] = fmaf(dx, Bk[r0], a * s[i]);
-                    part0 = fmaf(s[i], Ck[r0], part0);
-                }
-                if (r1 < N) {
-                    s[i + 1] = fmaf(dx, Bk[r1], a * s[i + 1]);
-                    part1 = fmaf(s[i + 1], Ck[r1], part1);
-                }
+                s[i] = fmaf(dx, bv[i], a * s[i]);
+                part0 = fmaf(s[i], cv[i], part0);
+                s[i + 1] = fmaf(dx, bv[i + 1], a * s[i + 1]);
+                part1 = fmaf(s[i + 1], cv[i + 1], part1);
             }
             const float part = rec_group_sum(part0 + part1);
             if (lane == 0 && live) y[(size_t)(first + c0 + k) * inner + h * P + p] = fmaf(skip, x, part);
@@ -261,18 +303,13 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
         __syncthreads();                                         // this buffer may be filled again; the next one's scalars are written
     }
-    if (live) {
-#pragma unroll
-        for (int i = 0; i < K; ++i) {
-            const int r = lane + i * REC_LANES;
-            if (r < N) S[r] = s[i];
-        }
-    }
+    if (live) rec_store_column<K>(s, S, lane, N);
 }
 
 // Tokens staged at a time: 16 where two buffers of them fit the default 48 KB of shared memory, else 8.
+static int rec_padded(int rows) { return rows <= 8 * REC_LANES ? 8 * REC_LANES : rows <= 16 * REC_LANES ? 16 * REC_LANES : 32 * REC_LANES; }
 static int rec_chunk(int rows) { return rows <= 128 ? REC_CHUNK : REC_CHUNK / 2; }
-static size_t rec_shared_bytes(int rows, int chunk) { return (size_t)2 * (2 * chunk * rows + chunk * REC_COLS + 2 * chunk) * sizeof(float); }
+static size_t rec_shared_bytes(int rows, int chunk) { return (size_t)2 * (2 * chunk * rec_padded(rows) + chunk * REC_COLS + 2 * chunk) * sizeof(float); }
 static bool rec_aligned(const void* p, int a, int b, int c, int d) { return (((uintptr_t)p & 15) == 0) && !((a | b | c | d) & 3); }
 
 extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
@@ -310,8 +347,10 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ __align__(16) float rec_shared[];
-    // two buffers of: q [chunk][D], k [chunk][D], v [chunk][REC_COLS], decay [chunk], beta [chunk]
-    const int buffer_floats = 2 * chunk * D + chunk * REC_COLS + 2 * chunk;
+    // two buffers of: q [chunk][DP], k [chunk][DP], v [chunk][REC_COLS], decay [chunk], beta [chunk]; rows are padded to
+    // DP = K * REC_LANES numbers and the padding is zero
+    constexpr int DP = K * REC_LANES;
+    const int buffer_floats = 2 * chunk * DP + chunk * REC_COLS + 2 * chunk;
     const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
@@ -328,9 +367,9 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
     auto stage = [&](int c0, float* base) {
         const int count = min(chunk, n - c0);
         const float* row = qkv + (size_t)(first + c0) * qkv_cols;
-        rec_stage(base, D, row + g * D, qkv_cols, count, D, vec);
-        rec_stage(base + chunk * D, D, row + k_off + g * D, qkv_cols, count, D, vec);
-        rec_stage(base + 2 * chunk * D, REC_COLS, row + v_off + h * V + p0, qkv_cols, count, width, vec_v);
+        rec_stage(base, DP, row + g * D, qkv_cols, count, D, vec);
+        rec_stage(base + chunk * DP, DP, row + k_off + g * D, qkv_cols, count, D, vec);
+        rec_stage(base + 2 * chunk * DP, REC_COLS, row + v_off + h * V + p0, qkv_cols, count, width, vec_v);
         rec_commit();
     };
     auto raw_pair = [&](int c0) {                                // this thread's token of the chunk: raw write strength, raw decay input
@@ -338,18 +377,16 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         return make_float2(rec_sum_slices(row + b_col + h, splits, split_stride), rec_sum_slices(row + a_col + h, splits, split_stride));
     };
     auto put_scalars = [&](float* base, float2 raw) {
-        base[2 * chunk * D + chunk * REC_COLS + threadIdx.x] = expf(neg_a * rec_softplus(raw.y + bias));
-        base[2 * chunk * D + chunk * REC_COLS + chunk + threadIdx.x] = 1.0f / (1.0f + expf(-raw.x));
+        base[2 * chunk * DP + chunk * REC_COLS + threadIdx.x] = expf(neg_a * rec_softplus(raw.y + bias));
+        base[2 * chunk * DP + chunk * REC_COLS + chunk + threadIdx.x] = 1.0f / (1.0f + expf(-raw.x));
     };
 
+    for (int e = threadIdx.x; e < 2 * buffer_floats; e += blockDim.x) rec_shared[e] = 0.0f;
+    __syncthreads();
     stage(0, rec_shared);
     float* S = state + (((size_t)slots[b] * heads + h) * V + (live ? p : 0)) * D;
     float s[K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) {
-        const int r = lane + i * REC_LANES;
-        s[i] = (live && r < D) ? S[r] : 0.0f;
-    }
+    rec_load_column<K>(s, S, lane, D, live);
     if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_pair(0));
     int it = 0;
     for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
@@ -367,37 +404,40 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         }
         __syncthreads();
         float* qs = cur;
-        float* ks = cur + chunk * D;
+        float* ks = cur + chunk * DP;
         // a warp per (token, q or k): sum of squares, scale to unit length (q also by D^-1/2)
         for (int item = warp; item < 2 * count; item += warps) {
-            float* vecp = (item & 1 ? ks : qs) + (item >> 1) * D;
+            float* vecp = (item & 1 ? ks : qs) + (item >> 1) * DP;
             float sumsq = 0.0f;
             for (int r = wlane; r < D; r += 32) sumsq = fmaf(vecp[r], vecp[r], sumsq);
             const float scale = rsqrtf(tt_warp_sum(sumsq) + 1e-6f) * (item & 1 ? 1.0f : q_scale);
             for (int r = wlane; r < D; r += 32) vecp[r] *= scale;
         }
         __syncthreads();
-        const float* vs = cur + 2 * chunk * D;
+        const float* vs = cur + 2 * chunk * DP;
         const float* decay = vs + chunk * REC_COLS;
         const float* beta = decay + chunk;
         for (int k = 0; k < count; ++k) {
             const float a = decay[k];
-            const float* qk = qs + k * D;
-            const float* kk = ks + k * D;
+            float kv[K], qv[K];                                  // all of the token's loads are asked for before the arithmetic
+            rec_load_vector<K>(kv, ks + k * DP, lane);
+            rec_load_vector<K>(qv, qs + k * DP, lane);
             float part0 = 0.0f, part1 = 0.0f;
 #pragma unroll
             for (int i = 0; i < K; i += 2) {
-                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
-                if (r0 < D) { s[i] *= a; part0 = fmaf(s[i], kk[r0], part0); }
-                if (r1 < D) { s[i + 1] *= a; part1 = fmaf(s[i + 1], kk[r1], part1); }
+                s[i] *= a;
+                part0 = fmaf(s[i], kv[i], part0);
+                s[i + 1] *= a;
+                part1 = fmaf(s[i + 1], kv[i + 1], part1);
             }
             const float u = beta[k] * ((live ? vs[k * REC_COLS + col] : 0.0f) - rec_group_sum(part0 + part1));
             part0 = 0.0f, part1 = 0.0f;
 #pragma unroll
             for (int i = 0; i < K; i += 2) {
-                const int r0 = lane + i * REC_LANES, r1 = r0 + REC_LANES;
-                if (r0 < D) { s[i] = fmaf(kk[r0], u, s[i]); part0 = fmaf(s[i], qk[r0], part0); }
-                if (r1 < D) { s[i + 1] = fmaf(kk[r1], u, s[i + 1]); part1 = fmaf(s[i + 1], qk[r1], part1); }
+                s[i] = fmaf(kv[i], u, s[i]);
+                part0 = fmaf(s[i], qv[i], part0);
+                s[i + 1] = fmaf(kv[i + 1], u, s[i + 1]);
+                part1 = fmaf(s[i + 1], qv[i + 1], part1);
             }
             const float part = rec_group_sum(part0 + part1);
             if (lane == 0 && live) o[(size_t)(first + c0 + k) * (heads * V) + h * V + p] = part;
@@ -405,13 +445,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
         __syncthreads();
     }
-    if (live) {
-#pragma unroll
-        for (int i = 0; i < K; ++i) {
-            const int r = lane + i * REC_LANES;
-            if (r < D) S[r] = s[i];
-        }
-    }
+    if (live) rec_store_column<K>(s, S, lane, D);
 }
 
 extern "C" int tt_delta_scan(const float* qkv, int qkv_cols, const float* proj, int splits, long long split_stride, int cols,
