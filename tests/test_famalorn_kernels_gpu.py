@@ -304,8 +304,13 @@ def test_norm_rotation_append_and_sink_attention(dtype, unit_norm, heads, kv_hea
         tokens = x.shape[0]
         q_out = torch.empty(tokens, heads * dim, dtype=dtype, device=DEV)
         cu, before = cu_of(news), torch.tensor(befores, dtype=torch.int32, device=DEV)
+        cos_sin = where = None
+        if rot and not decode:          # prompts look positions, cosines and sines up in the step's table; decoding computes them
+            cos_sin = torch.empty(tokens, rot // 2, 2, dtype=torch.float32, device=DEV)
+            where = torch.empty(tokens, 2, dtype=torch.int32, device=DEV)
+            api.rope_table(inv_freq.to(DEV), rot, cu, before, len(news), tokens, cos_sin, where)
         api.qk_norm_rope_append(slices(x, 2, 84).to(DEV), q_norm.to(DEV), k_norm.to(DEV), eps, inv_freq.to(DEV), rot, interleaved, 1.0, q_out,
-                                k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, vdim, status)
+                                k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, vdim, status, cos_sin, where)
         out = torch.empty(tokens, heads * vdim, dtype=dtype, device=DEV)
         if kernels == "tensor" and not decode:              # prompts: both products on the tcgen05 tensor cores
             api.attention_tcgen05(q_out, k_pool, v_pool, table, cu, before, len(news), tokens, heads, kv_heads, dim, scale, 0, out, status,

@@ -515,7 +515,8 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
                                            TAct* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                                            int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before,
                                            int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
-                                           int write_cache, unsigned* status) {
+                                           int write_cache, const float2* __restrict__ cos_sin, const int2* __restrict__ where,
+                                           unsigned* status) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ float head_shared[];          // QK_WARPS * max(head_dim, value_dim)
@@ -524,8 +525,10 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
     const long long w = (long long)blockIdx.x * QK_WARPS + warp;
     if (w >= (long long)n_tokens * items) return;
     const int t = (int)(w / items), item = (int)(w - (long long)t * items);
-    const int b = tt_find_sequence(cu, sequences, t);
-    const int pos = len_before[b] + (t - cu[b]);
+    // with the step's table (see rope_table_kernel) the token's position, sequence, cosines and sines are looked up
+    int b, pos;
+    if (where) { const int2 at = where[t]; pos = at.x; b = at.y; }
+    else { b = tt_find_sequence(cu, sequences, t); pos = len_before[b] + (t - cu[b]); }
     const int* table_row = table + (size_t)b * table_width;
     const float* row = proj + (size_t)t * cols;
     const int q_cols = heads * head_dim, k_cols = kv_heads * head_dim;
@@ -566,7 +569,8 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
     for (int i = lane; i < half; i += 32) {
         const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
         float si, co;
-        sincosf(__ldg(inv_freq + i) * (float)pos, &si, &co);
+        if (cos_sin) { const float2 cs = cos_sin[(size_t)t * half + i]; co = cs.x; si = cs.y; }
+        else sincosf(__ldg(inv_freq + i) * (float)pos, &si, &co);
         co *= attention_scaling;
         si *= attention_scaling;
         const float a = x[ia], c = x[ib];
@@ -581,16 +585,20 @@ extern "C" int tt_qk_norm_rope_append(const float* proj, int splits, long long s
                                       float attention_scaling, void* q_out, void* k_pool, void* v_pool, int act_dtype,
                                       const int* table, int table_width, int pool_blocks, const int* cu, const int* len_before,
                                       int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
-                                      int write_cache, unsigned* status, cudaStream_t stream) {
+                                      int write_cache, const void* cos_sin_table, const void* where_table, unsigned* status,
+                                      cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    const float2* cos_sin = (const float2*)cos_sin_table;        // both or neither: the step's rope table
+    const int2* where = (const int2*)where_table;
+    if ((cos_sin == nullptr) != (where == nullptr)) return (int)cudaErrorInvalidValue;
     if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim || head_dim <= 0 || value_dim <= 0) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)n_tokens * (heads + (write_cache ? 2 * kv_heads : 0));
     const unsigned blocks = (unsigned)((warps + QK_WARPS - 1) / QK_WARPS);
     const size_t shared = (size_t)QK_WARPS * (head_dim > value_dim ? head_dim : value_dim) * sizeof(float);
     if (act_dtype == TT_F32)
-        tt_launch_pdl(qk_norm_rope_append_kernel<float>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, status);
+        tt_launch_pdl(qk_norm_rope_append_kernel<float>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, status);
     else
-        tt_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, status);
+        tt_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, status);
     TT_LAUNCH_CHECK();
 }
 

@@ -128,27 +128,61 @@ __device__ __forceinline__ float rec_group_sum(float v) {
 // and channel), because the outputs of a sequence's first tokens read the state that the update
 // overwrites.  One token per sequence: a thread per (sequence, channel) does both.
 // ------------------------------------------------------------------------------------
+constexpr int CONV_TILE = 16;       // packed tokens a thread walks with its channel's last inputs in registers
+
+// A thread takes one channel through CONV_TILE packed tokens: every input is read once (plus taps - 1 at the tile's
+// start) and the window of the last inputs slides through registers.  Where the tile crosses into the next sequence
+// the window is filled from that sequence's state.
 __global__ void causal_conv_kernel(const float* __restrict__ proj, int splits, size_t split_stride, int cols, int col_off,
                                    int channels, const float* __restrict__ weight, const float* __restrict__ bias, int taps,
                                    int activation, const float* __restrict__ state, size_t slot_stride, float* __restrict__ out,
                                    const int* __restrict__ cu, const int* __restrict__ slots, int sequences, int n_tokens) {
     tt_pdl_launch_dependents();
-    tt_pdl_wait();
-    const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= channels) return;
-    const int b = tt_find_sequence(cu, sequences, t);
-    const int first = cu[b];
-    const int i = t - first;
-    const float* st = state + (size_t)slots[b] * slot_stride;
-    float acc = bias ? __ldg(bias + c) : 0.0f;
-    for (int j = 0; j < taps; ++j) {
-        const int s = i - (taps - 1) + j;
-        const float x = s >= 0 ? rec_sum_slices(proj + (size_t)(first + s) * cols + col_off + c, splits, split_stride)
-                               : st[(size_t)(taps - 1 + s) * channels + c];
-        acc = fmaf(__ldg(weight + (size_t)c * taps + j), x, acc);
+    const int keep = taps - 1;
+    float w[CONV_MAX_TAPS];
+    float shift = 0.0f;
+    if (c < channels) {                                          // filters are written by no kernel: fetched before the wait
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < taps ? __ldg(weight + (size_t)c * taps + j) : 0.0f;
+        shift = bias ? __ldg(bias + c) : 0.0f;
     }
-    out[(size_t)t * channels + c] = activation ? rec_silu(acc) : acc;
+    tt_pdl_wait();
+    if (c >= channels) return;
+    const int t0 = blockIdx.x * CONV_TILE, t1 = min(t0 + CONV_TILE, n_tokens);
+    int b = tt_find_sequence(cu, sequences, t0);
+    int first = cu[b], next = cu[b + 1];
+    float win[CONV_MAX_TAPS];                                    // win[j], j < keep: the input (keep - j) tokens back
+    auto fill = [&](int t) {                                     // the window as it stands before token t of sequence b
+        const float* st = state + (size_t)slots[b] * slot_stride;
+        const int i = t - first;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < keep) {
+                const int s = i - keep + j;
+                win[j] = s >= 0 ? rec_sum_slices(proj + (size_t)(first + s) * cols + col_off + c, splits, split_stride)
+                                : st[(size_t)(keep + s) * channels + c];
+            }
+        }
+    };
+    fill(t0);
+    for (int t = t0; t < t1; ++t) {
+        if (t == next) {                                         // the next sequence starts here
+            ++b;
+            first = next;
+            next = cu[b + 1];
+            fill(t);
+        }
+        const float x = rec_sum_slices(proj + (size_t)t * cols + col_off + c, splits, split_stride);
+        float acc = shift;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+            if (j <= keep) acc = fmaf(w[j], j < keep ? win[j] : x, acc);     // oldest input first, the token's own last
+        out[(size_t)t * channels + c] = activation ? rec_silu(acc) : acc;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < keep) win[j] = j + 1 < keep ? win[j + 1] : x;
+    }
 }
 
 // compute != 0: the sequence brings one token, whose output is computed here too
@@ -196,7 +230,7 @@ extern "C" int tt_causal_conv(const float* proj, int splits, long long split_str
     const unsigned bx = (unsigned)((channels + threads - 1) / threads);
     if (taps < 1 || taps > CONV_MAX_TAPS || bx > 65535) return (int)cudaErrorInvalidValue;
     if (!one_token_each) {
-        tt_launch_pdl(causal_conv_kernel, dim3(n_tokens, bx), dim3(threads), 0, stream, proj, splits, (size_t)split_stride, cols, col_off,
+        tt_launch_pdl(causal_conv_kernel, dim3((n_tokens + CONV_TILE - 1) / CONV_TILE, bx), dim3(threads), 0, stream, proj, splits, (size_t)split_stride, cols, col_off,
                       channels, weight, bias, taps, activation, (const float*)state, (size_t)slot_stride, out, cu, slots, sequences, n_tokens);
     }
     if (taps > 1 || one_token_each)

@@ -214,12 +214,14 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
                         inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool, attention_scaling: float, q_out: torch.Tensor,
                         k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, table: torch.Tensor, cu: torch.Tensor,
                         len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
-                        value_dim: int, status: torch.Tensor) -> None:
+                        value_dim: int, status: torch.Tensor, cos_sin: torch.Tensor | None = None,
+                        where: torch.Tensor | None = None) -> None:
     """The general form of :func:`rope_append`: float32 partial sums ``proj`` [splits, tokens, cols] hold q heads, then k
     heads (``head_dim`` numbers each), then v heads (``value_dim`` each).  q and k are normalised per head (x / rms(x) *
     weight; ``q_norm`` / ``k_norm`` float32 [head_dim] or None), then their first ``rotary_dim`` numbers are rotated, in
     neighbouring pairs (``interleaved``) or in halves; q goes to ``q_out``, k and v to the block pools.  Without pools
-    the projection holds queries only."""
+    the projection holds queries only.  ``cos_sin`` and ``where``: the step's :func:`rope_table` for this layer's
+    frequencies, looked up instead of computing positions, cosines and sines per head."""
     _need(proj, torch.float32, "projection")
     _need(inv_freq, torch.float32, "inv_freq")
     write = k_pool is not None
@@ -235,13 +237,20 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
         raise KernelError("cache pools and activations must share a dtype")
     if rotary_dim and inv_freq.numel() < rotary_dim // 2:
         raise KernelError("the rotary table is shorter than half the rotary part")
+    if (cos_sin is None) != (where is None):
+        raise KernelError("the step's rope table comes as both of cos_sin and where, or neither")
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos/sin table")
+        _need(where, torch.int32, "token positions")
+        if tuple(cos_sin.shape) != (n_tokens, rotary_dim // 2, 2) or tuple(where.shape) != (n_tokens, 2):
+            raise KernelError("the rope table does not fit the step")
     fn = _fn("elementwise", "tt_qk_norm_rope_append", [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(proj), proj.shape[0], proj.stride(0), cols, _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(inv_freq), rotary_dim,
               1 if interleaved else 0, attention_scaling, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), dtype_code(q_out.dtype), _ptr(table),
               table.shape[1], k_pool.shape[0] if write else 0, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim,
-              value_dim, 1 if write else 0, _ptr(status), _stream()), "qk_norm_rope_append")
+              value_dim, 1 if write else 0, _ptr(cos_sin), _ptr(where), _ptr(status), _stream()), "qk_norm_rope_append")
 
 
 def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, q_out: torch.Tensor,

@@ -141,10 +141,12 @@ class CausalAttention(Mixer):
         if self.general:
             projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
             q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
+            # prompts: positions, cosines and sines come from the step's table, made once for all layers and heads
+            cos_sin, where = self.step_rope_table(ctx) if (rot.rotary_dim and not ctx.decode) else (None, None)
             api.qk_norm_rope_append(projection, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq, rot.rotary_dim,
                                     rot.interleaved, rot.attention_scaling, q, cache.k_pool if cache.writes else None,
                                     cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
-                                    self.heads, self.kv_heads, self.head_dim, self.value_dim, ctx.status)
+                                    self.heads, self.kv_heads, self.head_dim, self.value_dim, ctx.status, cos_sin, where)
             self.attend(ctx, q, cache, table, mixed)
             return self.out.delta(ctx, mixed, "attention.out")
         if (cache.writes and not ctx.decode and x.dtype == torch.bfloat16
