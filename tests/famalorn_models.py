@@ -132,3 +132,20 @@ def oracle_logits(folder: Path, tokens: list[int]) -> torch.Tensor:
         with torch.no_grad():
             _oracle[key] = plain_famalorn.forward(cfg, weights, tokens)
     return _oracle[key]
+
+
+def oracle_sensitivity(folder: Path, tokens: list[int]) -> torch.Tensor:
+    """Per position, one minus the cosine between the plain implementation's logits and its logits with every operand of
+    a matrix product (and queries, keys and values) narrowed to bfloat16 on the way, everything else as exact as before:
+    how far the rounding of activations alone carries that position.  Positions where a norm divides by a nearly
+    vanishing vector, or a gate sits at its kink, move a hundred times further than the others."""
+    import plain_famalorn
+
+    key = ("sensitivity", str(folder), tuple(tokens))
+    if key not in _oracle:
+        want = oracle_logits(folder, tokens)
+        cfg, weights = _oracle[("model", str(folder))]
+        with torch.no_grad():
+            other = plain_famalorn.forward(cfg, weights, tokens, narrow=lambda x: x.to(torch.bfloat16).to(x.dtype))
+        _oracle[key] = 1.0 - torch.nn.functional.cosine_similarity(want, other, dim=-1)
+    return _oracle[key]

@@ -24,6 +24,16 @@ from pathlib import Path
 import numpy as np
 import torch
 
+# What stands in for the narrowing of activations: None (exact), or a function applied wherever an engine that
+# multiplies bfloat16 matrices has to narrow its operand (the input of every projection, queries, keys and values on
+# their way to the scores, the read-outs before the output projections).  ``forward(..., narrow=f)`` sets it.
+_narrow = None
+
+
+def nar(x):
+    return x if _narrow is None else _narrow(x)
+
+
 _NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64}
 
 
@@ -95,7 +105,7 @@ def mamba2(h, p, w, prefix, eps):
     H, P, N, G = p["heads"], p["vdim"], p["state"], p["groups"]
     inner = H * P
     T = h.shape[0]
-    proj = h @ w[prefix + "in"].T
+    proj = nar(h) @ w[prefix + "in"].T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     xbc = silu(causal_conv(xbc, w[prefix + "conv"], w[prefix + "conv.b"]))
     x = xbc[:, :inner].reshape(T, H, P)
@@ -113,7 +123,7 @@ def mamba2(h, p, w, prefix, eps):
     y = y.reshape(T, inner) * silu(z)
     parts = p["norm_groups"]
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[prefix + "norm"]
-    return y @ w[prefix + "o"].T
+    return nar(y) @ w[prefix + "o"].T
 
 
 def rotate_interleaved(x, positions, dims, base):
@@ -134,9 +144,10 @@ def rotate_interleaved(x, positions, dims, base):
 def sink_attention(h, p, w, prefix, eps):
     H, G, D, V = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
     T = h.shape[0]
+    h = nar(h)
     q = (h @ w[prefix + "q"].T).reshape(T, H, D)
     k = (h @ w[prefix + "k"].T).reshape(T, G, D)
-    v = (h @ w[prefix + "v"].T).reshape(T, G, V)
+    v = nar((h @ w[prefix + "v"].T).reshape(T, G, V))
     q = rms(q, eps) * w[prefix + "q.norm"]
     k = rms(k, eps) * w[prefix + "k.norm"]
     rot = p.get("rot")
@@ -144,6 +155,7 @@ def sink_attention(h, p, w, prefix, eps):
         pos = torch.arange(T)
         q = rotate_interleaved(q, pos, rot["dims"], rot["base"])
         k = rotate_interleaved(k, pos, rot["dims"], rot["base"])
+    q, k = nar(q), nar(k)
     out = torch.zeros(T, H, V, dtype=h.dtype)
     for head in range(H):
         g = head // (H // G)
@@ -153,7 +165,7 @@ def sink_attention(h, p, w, prefix, eps):
             m = torch.maximum(s.max(), sink)
             e = torch.exp(s - m)
             out[t, head] = (e[:, None] * v[:t + 1, g]).sum(0) / (e.sum() + torch.exp(sink - m))
-    return out.reshape(T, H * V) @ w[prefix + "o"].T
+    return nar(out.reshape(T, H * V)) @ w[prefix + "o"].T
 
 
 def parallel(h, p, w, prefix, eps):
@@ -164,6 +176,7 @@ def parallel(h, p, w, prefix, eps):
 def gated_delta(h, p, w, prefix, eps):
     H, G, D, V = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
     T = h.shape[0]
+    h = nar(h)
     q = silu(causal_conv(h @ w[prefix + "q"].T, w[prefix + "q.conv"])).reshape(T, G, D)
     k = silu(causal_conv(h @ w[prefix + "k"].T, w[prefix + "k.conv"])).reshape(T, G, D)
     v = silu(causal_conv(h @ w[prefix + "v"].T, w[prefix + "v.conv"])).reshape(T, H, V)
@@ -182,19 +195,30 @@ def gated_delta(h, p, w, prefix, eps):
             S = S + torch.outer(k[t, g], u)
             o[t, head] = S.T @ q[t, g]
     o = rms(o, eps) * w[prefix + "norm"] * gate
-    return o.reshape(T, H * V) @ w[prefix + "o"].T
+    return nar(o.reshape(T, H * V)) @ w[prefix + "o"].T
 
 
 def dense_ffn(h, w, prefix):
-    return (torch.relu(h @ w[prefix + "gate"].T) * (h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
+    h = nar(h)
+    return nar(torch.relu(h @ w[prefix + "gate"].T) * (h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
 
 
 MIXERS = {"mamba2": mamba2, "parallel": parallel, "delta": gated_delta}
 
 
 # ------------------------------------------------------------------------ whole model
-def forward(cfg, w, tokens, dtype=torch.float64, layers_out: list | None = None):
-    """Logits [T, vocab] for one whole sequence; ``layers_out`` collects the stream after each layer."""
+def forward(cfg, w, tokens, dtype=torch.float64, layers_out: list | None = None, narrow=None):
+    """Logits [T, vocab] for one whole sequence; ``layers_out`` collects the stream after each layer.  ``narrow``: see
+    ``_narrow`` (for measuring how far the rounding of activations alone moves a position's logits)."""
+    global _narrow
+    _narrow = narrow
+    try:
+        return _forward(cfg, w, tokens, dtype, layers_out)
+    finally:
+        _narrow = None
+
+
+def _forward(cfg, w, tokens, dtype, layers_out):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -205,4 +229,4 @@ def forward(cfg, w, tokens, dtype=torch.float64, layers_out: list | None = None)
             x = x + dense_ffn(layer_norm(x, w[pre + "norm2"], eps), w, pre + "mlp.")
         if layers_out is not None:
             layers_out.append(x.clone())
-    return layer_norm(x, w["final.norm"], eps) @ w["head"].T
+    return nar(layer_norm(x, w["final.norm"], eps)) @ w["head"].T

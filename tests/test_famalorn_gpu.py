@@ -40,38 +40,40 @@ def load(folder, dtype):
 
 
 class Judge:
-    """Collects a test's rows and judges them.  float32: every logit within 5e-5 of the request's largest one, at once
-    (the exact path is held much closer than the Llama tests' shared bound).  bfloat16: these models' large random
-    weights carry rounding into exponentials, gates and norms of nearly vanishing vectors, so single positions stray and
-    a recurrent state carries a stray value on (measured: mean cosine 0.9999, single positions down to 0.98, positions
-    where float32 has its own largest error; the same bits whether a position was computed in a prompt, a portion or
-    decoded).  A fault of the cache or of a state moves whole requests much further.  So over all rows of a test: none
-    below 0.95, at most one in twenty (or two) below 0.999, mean at least 0.999."""
+    """Compares rows of logits with the plain implementation's.  float32: every logit within 5e-5 of the request's
+    largest one (the exact path is held much closer than the Llama tests' shared bound).  bfloat16: the cosine with the
+    plain logits, position by position, against a bound that knows how far rounding alone carries that position:
+    ``1 - cos <= 1e-3 + 4 * s``, s being the plain implementation's own movement when it narrows its activations to
+    bfloat16 where an engine has to (``oracle_sensitivity``).  These models' large random weights make some positions ill-conditioned (a
+    norm of a nearly vanishing vector, a gate at its kink): there s reaches a few hundredths and float32 has its own
+    largest error; everywhere else s is about 1e-5 and the bound is the 0.999 of the Llama tests.  A fault of the cache or
+    of a state moves well-conditioned positions by far more.  Over a test, the mean cosine must be at least 0.998."""
 
-    def __init__(self, dtype):
-        self.dtype, self.cos, self.names = dtype, [], []
+    def __init__(self, dtype, folder):
+        self.dtype, self.folder, self.cos = dtype, folder, []
 
-    def add(self, got, want, what):
-        got, want = got.double().cpu().reshape(-1, got.shape[-1]), want.double().reshape(-1, want.shape[-1])
+    def add(self, got, tokens, rows, what):
+        rows = list(rows)
+        want = oracle_logits(self.folder, tokens)[rows]
+        got = got.double().cpu().reshape(-1, got.shape[-1])
         assert got.shape == want.shape and torch.isfinite(got).all(), what
         if self.dtype == "float32":
             scale = max(1.0, float(want.abs().max()))
             err = float((got - want).abs().max())
             assert err <= 5e-5 * scale, f"{what}: max |diff| {err:.3e} with logits up to {scale:.3f}"
             return
-        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
-        self.cos.append(cos)
-        self.names += [what] * len(cos)
+        from famalorn_models import oracle_sensitivity
+
+        away = 1.0 - torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        bound = 1e-3 + 4.0 * oracle_sensitivity(self.folder, tokens)[rows]
+        worst = int((away / bound).argmax())
+        assert bool((away <= bound).all()), (f"{what}: position {rows[worst]} has cosine {1 - float(away[worst]):.5f}, "
+                                              f"rounding alone allows {1 - float(bound[worst]):.5f}")
+        self.cos.append(1.0 - away)
 
     def done(self):
-        if self.dtype == "float32":
-            return
-        cos = torch.cat(self.cos)
-        worst = int(cos.argmin())
-        assert float(cos.min()) >= 0.95, f"{self.names[worst]}: cosine {float(cos.min()):.5f}"
-        low = int((cos < 0.999).sum())
-        assert low <= max(2, len(cos) // 20), f"{low} of {len(cos)} rows below 0.999, the worst in {self.names[worst]}"
-        assert float(cos.mean()) >= 0.999, f"mean cosine {float(cos.mean()):.5f}"
+        if self.dtype == "bfloat16":
+            assert float(torch.cat(self.cos).mean()) >= 0.998, f"mean cosine {float(torch.cat(self.cos).mean()):.5f}"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -81,7 +83,7 @@ def test_whole_prompts_alone(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=2)
     for seed, length in enumerate([1, 2, 3, 15, 16, 17, 63, 64, 65, 129, 200]):
         tokens = token_ids(CONFIGS[name]["vocab"], length, 100 + seed)
@@ -89,7 +91,7 @@ def test_whole_prompts_alone(folders, name, dtype):
         logits = engine.step([Entry(slot, tokens, list(range(length)))])
         engine.close(slot)
         engine.check_status()
-        judge.add(logits, oracle_logits(folder, tokens), f"{name} whole length {length}")
+        judge.add(logits, tokens, range(length), f"{name} whole length {length}")
     assert engine.cache.free_blocks == engine.cache.num_blocks
     judge.done()
 
@@ -102,7 +104,7 @@ def test_prompt_in_portions(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=2)
     tokens = token_ids(CONFIGS[name]["vocab"], 150, 210)
     want = oracle_logits(folder, tokens)
@@ -115,7 +117,7 @@ def test_prompt_in_portions(folders, name, dtype):
             at += count
         engine.close(slot)
         engine.check_status()
-        judge.add(torch.cat(got), want, f"{name} portions {cuts}")
+        judge.add(torch.cat(got), tokens, range(len(tokens)), f"{name} portions {cuts}")
     judge.done()
 
 
@@ -126,15 +128,15 @@ def test_pieces_of_a_step(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     runtime = load(folder, dtype)
     engine = runtime.new_engine(max_tokens=512, max_sequences=3, max_step_tokens=50)
     prompts = [token_ids(CONFIGS[name]["vocab"], n, 220 + n) for n in (70, 9, 45)]
     slots = [engine.open() for _ in prompts]
     logits = engine.step([Entry(s, p, [0, len(p) // 2, len(p) - 1]) for s, p in zip(slots, prompts)])
     engine.check_status()
-    want = torch.cat([oracle_logits(folder, p)[[0, len(p) // 2, len(p) - 1]] for p in prompts])
-    judge.add(logits, want, f"{name} pieces")
+    for i, p in enumerate(prompts):
+        judge.add(logits[3 * i: 3 * i + 3], p, [0, len(p) // 2, len(p) - 1], f"{name} pieces, prompt {i}")
     judge.done()
 
 
@@ -144,7 +146,7 @@ def test_last_tokens_and_first_tokens_one_by_one(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=2)
     vocab = CONFIGS[name]["vocab"]
     for seed, length in enumerate([40, 97]):            # the longer one decodes across a block border
@@ -157,12 +159,12 @@ def test_last_tokens_and_first_tokens_one_by_one(folders, name, dtype):
             got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
         engine.close(slot)
         engine.check_status()
-        judge.add(torch.cat(got), want[head - 1:], f"{name} tail of length {length}")
+        judge.add(torch.cat(got), tokens, range(head - 1, length), f"{name} tail of length {length}")
     tokens = token_ids(vocab, 12, 240)                  # from an empty slot, token by token
     slot = engine.open()
     got = [engine.step([Entry(slot, [t], [0])]) for t in tokens]
     engine.close(slot)
-    judge.add(torch.cat(got), oracle_logits(folder, tokens), f"{name} first tokens")
+    judge.add(torch.cat(got), tokens, range(len(tokens)), f"{name} first tokens")
     judge.done()
 
 
@@ -175,7 +177,7 @@ def test_unequal_batches_with_reuse(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     vocab = CONFIGS[name]["vocab"]
     batches = [
         [(5, 9), (9, 40), (2, 2), (17, 30)],
@@ -207,8 +209,7 @@ def test_unequal_batches_with_reuse(folders, name, dtype):
                 r["at"] += 1
         engine.check_status()
         for r, (prompt_len, total) in zip(requests, batch):
-            want = oracle_logits(folder, r["tokens"])[prompt_len - 1:]
-            judge.add(torch.stack(r["got"]), want, f"{name} request {prompt_len}->{total} in a batch")
+            judge.add(torch.stack(r["got"]), r["tokens"], range(prompt_len - 1, total), f"{name} request {prompt_len}->{total} in a batch")
     assert engine.cache.free_blocks == engine.cache.num_blocks
     judge.done()
 
@@ -221,7 +222,7 @@ def test_long_decoding_with_slow_decay(folders, name, dtype):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, dtype, slow_decay=True)
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=2)
     tokens = token_ids(CONFIGS[name]["vocab"], 330, 400)
     want = oracle_logits(folder, tokens)
@@ -234,7 +235,7 @@ def test_long_decoding_with_slow_decay(folders, name, dtype):
     engine.close(slot)
     engine.check_status()
     assert engine.graph_replays > 100
-    judge.add(torch.cat(got), want[179:], f"{name} long decoding")
+    judge.add(torch.cat(got), tokens, range(179, 330), f"{name} long decoding")
     judge.done()
 
 
@@ -299,7 +300,7 @@ def test_trace_replay_as_a_subprocess(folders, tmp_path, name, dtype):
     vocab = CONFIGS[name]["vocab"]
     requests = {f"q{i}": token_ids(vocab, n, 700 + i) for i, n in enumerate([40, 9, 75, 66])}
     prompt_len = {"q0": 7, "q1": 1, "q2": 64, "q3": 60}
-    judge = Judge(dtype)
+    judge = Judge(dtype, folder)
     steps, expect, n = [], [], 0
     for batch in (["q0", "q2", "q1"], ["q3"]):
         at = {k: prompt_len[k] for k in batch}
@@ -325,8 +326,9 @@ def test_trace_replay_as_a_subprocess(folders, tmp_path, name, dtype):
         if not wanted:
             assert not (tmp_path / "out" / f"{step}.f32").exists()
             continue
-        want = torch.stack([oracle_logits(folder, requests[k])[place] for k, place in wanted])
-        judge.add(read_step(tmp_path / "out", step, vocab), want, f"{name} step {step}")
+        got = read_step(tmp_path / "out", step, vocab)
+        for row, (k, place) in enumerate(wanted):
+            judge.add(got[row: row + 1], requests[k], [place], f"{name} step {step} request {k}")
     judge.done()
 
 
@@ -349,3 +351,78 @@ def test_command_line(tmp_path):
     assert out["generated_token_ids"] == [sequence[5:]]
     bench = json.loads(cli("bench", str(folder), "--steps", "8", "--warmup", "3", "--prompt-len", "20", "--batch", "2", "--json"))
     assert bench["tokens_per_s"] > 0 and bench["prefill_tokens_per_s"] > 0
+
+
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: layer order, every size and every constant (sizes need not be multiples of
+    anything: widths that are no multiple of 8 run the exact product in bfloat16 too)."""
+    import random
+
+    r = random.Random(seed)
+
+    def mamba():
+        groups = r.choice([1, 2, 3])
+        heads = groups * r.choice([1, 2])
+        vdim = r.choice([6, 10, 16, 36])
+        norm_groups = r.choice([g for g in (1, 2, heads) if (heads * vdim) % g == 0])
+        return {"heads": heads, "vdim": vdim, "state": r.choice([5, 16, 40, 70, 130]), "groups": groups, "norm_groups": norm_groups,
+                "conv": r.choice([1, 2, 3, 4, 6])}
+
+    def delta():
+        kv = r.choice([1, 2])
+        return {"heads": kv * r.choice([1, 3]), "kv_heads": kv, "dim": r.choice([8, 20, 48, 96]), "vdim": r.choice([6, 16, 34]),
+                "conv": r.choice([2, 3, 4])}
+
+    def attention():
+        kv = r.choice([1, 2])
+        dim = r.choice([8, 12, 32, 64])
+        rot = r.choice([0, dim // 2 // 2 * 2, dim])
+        left = {"heads": kv * r.choice([1, 2, 4]), "kv_heads": kv, "dim": dim, "vdim": r.choice([dim, 10, 24]), "scale": r.choice([0.1, 0.3, dim ** -0.5])}
+        if rot:
+            left["rot"] = {"dims": rot, "base": r.choice([100.0, 10000.0, 1e6])}
+        return {"left": left, "right": mamba(), "left_scale": r.choice([0.5, 1.0, 1.7]), "right_scale": r.choice([0.6, 1.0, 1.4])}
+
+    layers = []
+    for _ in range(r.choice([2, 3, 4])):
+        kind = r.choice(["delta", "mamba2", "parallel"])
+        mixer = {"delta": delta, "mamba2": mamba, "parallel": attention}[kind]()
+        layers.append({"type": kind, "mixer": mixer, "mlp": r.choice([None, {"kind": "dense", "ff": r.choice([24, 50, 128])}])})
+    return {"architecture": "Famalorn", "vocab": r.choice([50, 129, 300]), "width": r.choice([40, 90, 100, 128]),
+            "norm": {"eps": r.choice([1e-6, 1e-5])}, "layers": layers}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", [11, 12, 13, 15, 16, 26, 27])
+def test_configurations_drawn_from_a_seed(tmp_path, seed, dtype):
+    """Whole, then a prompt and decoding beside a second request in the same batch, on models whose order of layers,
+    sizes and constants are drawn at random."""
+    import famalorn_models
+    from thintensor_b200.engine.engine import Entry
+
+    name = f"seed{seed}"
+    famalorn_models.CONFIGS[name], famalorn_models.SEEDS[name] = random_config(seed), seed
+    try:
+        folder = write_model(tmp_path / name, name, "float32" if dtype == "float32" else "bfloat16")
+        vocab = famalorn_models.CONFIGS[name]["vocab"]
+        engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=3)
+        judge = Judge(dtype, folder)
+        first, second = token_ids(vocab, 90, 800 + seed), token_ids(vocab, 70, 900 + seed)
+        slot = engine.open()
+        judge.add(engine.step([Entry(slot, first, list(range(90)))]), first, range(90), f"seed {seed} whole")
+        engine.close(slot)
+        a, b = engine.open(), engine.open()
+        got_a = [engine.step([Entry(a, first[:61], [60]), Entry(b, second[:3], [])])[0:1]]
+        got_b = []
+        for t in range(61, 90):
+            entries = [Entry(a, [first[t]], [0])]
+            if 3 + t - 61 < 70:
+                entries.append(Entry(b, [second[3 + t - 61]], [0]))
+            out = engine.step(entries)
+            got_a.append(out[0:1])
+            got_b.append(out[1:2])
+        engine.check_status()
+        judge.add(torch.cat(got_a), first, range(60, 90), f"seed {seed} first request")
+        judge.add(torch.cat(got_b), second, range(3, 3 + len(got_b)), f"seed {seed} second request")
+        judge.done()
+    finally:
+        del famalorn_models.CONFIGS[name], famalorn_models.SEEDS[name]
