@@ -108,23 +108,16 @@ def reference_arm(config: dict, steps: int, warmup: int) -> int:
     return 0
 
 
+FAMALORN_SHAPES = {"1b": "famalorn-w2048", "3b": "famalorn-w3072"}
+
+
 def famalorn_pair(size: str) -> tuple[dict, dict]:
-    """(Famalorn config.json, Llama config.json) of one size: the same width, feed-forward width, vocabulary and number of
-    layers; every Famalorn layer has the feed-forward, and its mixers (gated delta rule, Mamba-2, attention beside
-    Mamba-2, in turn) are sized like published models of their kinds at this width."""
-    width, ff, heads, kv_heads, head_dim, layers = {"1b": (2048, 8192, 32, 8, 64, 6), "3b": (3072, 8192, 24, 8, 128, 6)}[size]
+    """(Famalorn config.json, Llama config.json) of one size, both from the table of named shapes: the same width,
+    feed-forward width, vocabulary and number of layers; every Famalorn layer has the feed-forward, and its mixers (gated
+    delta rule, Mamba-2, attention beside Mamba-2, in turn) are sized like published models of their kinds at this width."""
+    famalorn = json.loads(json.dumps(SHAPES[FAMALORN_SHAPES[size]]))
     llama = dict(SHAPES[SHAPE_NAMES[size]])
-    llama["num_hidden_layers"] = layers
-    mlp = {"kind": "dense", "ff": ff}
-    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": width // 128, "kv_heads": width // 256, "dim": 128, "vdim": 128, "conv": 4}}
-    mamba = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}
-    pair = {"type": "parallel", "mlp": mlp, "mixer": {
-        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
-                 "rot": {"dims": head_dim // 2, "base": 500000.0}},
-        "right": {"heads": width // 64, "vdim": 64, "state": 64, "groups": 1, "norm_groups": 1, "conv": 4},
-        "left_scale": 1.0, "right_scale": 1.0}}
-    famalorn = {"architecture": "Famalorn", "vocab": llama["vocab_size"], "width": width, "norm": {"eps": 1e-6},
-                "layers": [[delta, mamba, pair][i % 3] for i in range(layers)]}
+    llama["num_hidden_layers"] = len(famalorn["layers"])
     return famalorn, llama
 
 

@@ -351,6 +351,8 @@ def test_command_line(tmp_path):
     assert out["generated_token_ids"] == [sequence[5:]]
     bench = json.loads(cli("bench", str(folder), "--steps", "8", "--warmup", "3", "--prompt-len", "20", "--batch", "2", "--json"))
     assert bench["tokens_per_s"] > 0 and bench["prefill_tokens_per_s"] > 0
+    report = json.loads(cli("validate", str(folder), "--dtype", "fp32", "--length", "80", "--json"))      # the ways of running against one another
+    assert report["tier"] == "exact_pass" and set(report["modes"]) == {"whole", "tail_by_one", "unequal_batch"}
 
 
 def random_config(seed: int) -> dict:

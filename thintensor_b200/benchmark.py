@@ -18,7 +18,8 @@ from .kernels import api
 from .sampling.sampler import SamplingParams
 
 # Named shapes for benchmarks with random weights, each a whole config.json: the three Llama 3
-# models the reference's reports measure and two tiny ones that differ in every size and option.
+# models the reference's reports measure, two tiny ones that differ in every size and option, and
+# two Famalorn models of six layers at the widths of the 1B and 3B Llama shapes.
 # They are data (config/shapes.json), read here and by bench.py.
 SHAPES: dict[str, dict] = json.loads((Path(__file__).resolve().parent / "config" / "shapes.json").read_text(encoding="utf-8"))
 
