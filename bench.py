@@ -140,6 +140,9 @@ def design_bench(args) -> int:
             prompts = [torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist() for _ in range(args.batch)]
             context = args.prompt_len + args.warmup + args.steps + 64
             prefill = measure_prefill(runtime, prompts[0], repeats=3, warmup=3)
+            # several prompts in one step (8,192 packed tokens at most): the recurrences run a CTA per sequence, head and
+            # 32 columns, so a batch of prompts is what fills the GPU with them
+            together = measure_prefill(runtime, prompts[:max(1, min(args.batch, 8192 // args.prompt_len))], repeats=3, warmup=3)
             decode = measure_decode(runtime, prompts, context, args.warmup, args.steps)
             spans = measure_classes(runtime, prompts, context, prefill_prompts=prompts[:1])
             achieved = decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9
@@ -147,6 +150,9 @@ def design_bench(args) -> int:
                 "layers": len(runtime.model.spec.layers),
                 "prefill": {"tokens": prefill["tokens"], "ms": round(prefill["ms"], 3), "tokens_per_s": round(prefill["tokens_per_s"], 1),
                             "tensor_frac": round(prefill["flops"] / (prefill["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+                "prefill_batch": {"sequences": together["sequences"], "tokens": together["tokens"], "ms": round(together["ms"], 3),
+                                  "tokens_per_s": round(together["tokens_per_s"], 1),
+                                  "tensor_frac": round(together["flops"] / (together["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
                 "decode": {"batch": args.batch, "ms_per_step": round(decode["ms_per_step"], 4), "tokens_per_s": round(decode["tokens_per_s"], 1),
                            "bytes_per_step": int(decode["bytes_per_step"]), "hbm_frac": round(achieved / pk["hbm_gbs"], 4),
                            "launches_per_step": decode["launches_per_step"]},

@@ -135,8 +135,10 @@ def mamba2_plain(x, B, C, dt, a_log, d_skip, S0):
     return y, S
 
 
-@pytest.mark.parametrize("heads,P,N,groups", [(4, 16, 24, 2), (2, 40, 72, 1), (3, 8, 136, 3), (6, 33, 5, 2)])
-def test_mamba2_scan(heads, P, N, groups):
+@pytest.mark.parametrize("form", ["narrow", "wide"])
+@pytest.mark.parametrize("heads,P,N,groups", [(4, 16, 24, 2), (2, 40, 72, 1), (3, 8, 136, 3), (6, 33, 5, 2), (2, 70, 128, 2)])
+def test_mamba2_scan(heads, P, N, groups, form):
+    """Both forms of the kernel (one column per lane group, or four; more than 128 state rows always run the first)."""
     from thintensor_b200.kernels import api
 
     inner, news, slot_ids = heads * P, [37, 1, 16], [3, 1, 0]
@@ -149,7 +151,7 @@ def test_mamba2_scan(heads, P, N, groups):
     before = state.clone()
     y = torch.empty(tokens, inner, dtype=torch.float32, device=DEV)
     api.mamba2_scan(xbc.to(DEV), slices(raw, 2, 56).to(DEV), dt_col, dt_bias.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, y, cu_of(news),
-                    torch.tensor(slot_ids, dtype=torch.int32, device=DEV), len(news), heads, P, N, groups)
+                    torch.tensor(slot_ids, dtype=torch.int32, device=DEV), len(news), heads, P, N, groups, form)
     at = 0
     for s, n in zip(slot_ids, news):
         rows = xbc[at: at + n].double()
@@ -164,8 +166,9 @@ def test_mamba2_scan(heads, P, N, groups):
     assert torch.equal(state[[2, 4]], before[[2, 4]])
 
 
-@pytest.mark.parametrize("heads,qk_heads,D,V", [(4, 2, 24, 40), (3, 1, 136, 8), (2, 2, 16, 16), (6, 3, 72, 33)])
-def test_delta_scan(heads, qk_heads, D, V):
+@pytest.mark.parametrize("form", ["narrow", "wide"])
+@pytest.mark.parametrize("heads,qk_heads,D,V", [(4, 2, 24, 40), (3, 1, 136, 8), (2, 2, 16, 16), (6, 3, 72, 33), (2, 1, 128, 70)])
+def test_delta_scan(heads, qk_heads, D, V, form):
     from thintensor_b200.kernels import api
 
     news, slot_ids = [29, 1, 16], [2, 0, 1]
@@ -178,7 +181,7 @@ def test_delta_scan(heads, qk_heads, D, V):
     before = state.clone()
     out = torch.empty(tokens, heads * V, dtype=torch.float32, device=DEV)
     api.delta_scan(qkv.to(DEV), slices(raw, 3, 65).to(DEV), b_col, a_col, dt_bias.to(DEV), a_log.to(DEV), state, out, cu_of(news),
-                   torch.tensor(slot_ids, dtype=torch.int32, device=DEV), len(news), heads, qk_heads, D, V)
+                   torch.tensor(slot_ids, dtype=torch.int32, device=DEV), len(news), heads, qk_heads, D, V, form)
     at = 0
     for s, n in zip(slot_ids, news):
         rows = qkv[at: at + n].double()

@@ -247,8 +247,11 @@ extern "C" int tt_causal_conv(const float* proj, int splits, long long split_str
 // xbc: float32 [tokens][inner + 2 * groups * N] (x, then B, then C: the convolution's output);
 // dt_raw: column dt_col of the projection's partial sums; state: [slots][heads][P][N].
 // ------------------------------------------------------------------------------------
-template <int K>
-__global__ void __launch_bounds__(REC_COLS* REC_LANES)
+// G column groups of REC_LANES lanes per CTA, each owning C neighbouring columns: (32, 1) gives a sequence the most
+// warps (one long prompt, decoding); (16, 4) reads a token's vectors from shared memory once for four columns, which is
+// what bounds the kernel once the grid fills the GPU (batches of prompts).
+template <int K, int G, int C>
+__global__ void __launch_bounds__(G* REC_LANES)
 mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __restrict__ proj, int splits, size_t split_stride,
                    int cols, int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                    const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
@@ -257,19 +260,17 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ __align__(16) float rec_shared[];
-    // two buffers of: B [chunk][NP], C [chunk][NP], x [chunk][REC_COLS], decay [chunk], step [chunk]; rows are padded to
+    // two buffers of: B [chunk][NP], C [chunk][NP], x [chunk][TILE], decay [chunk], step [chunk]; rows are padded to
     // NP = K * REC_LANES numbers and the padding is zero, so the token loop needs no bounds
-    constexpr int NP = K * REC_LANES;
-    const int buffer_floats = 2 * chunk * NP + chunk * REC_COLS + 2 * chunk;
-    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
+    constexpr int NP = K * REC_LANES, TILE = G * C;
+    const int buffer_floats = 2 * chunk * NP + chunk * TILE + 2 * chunk;
+    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * TILE;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
     const int g = h / (heads / groups);
     const int inner = heads * P;
-    const int lane = threadIdx.x % REC_LANES, col = threadIdx.x / REC_LANES;
-    const int p = p0 + col;
-    const bool live = p < P;
-    const int width = min(REC_COLS, P - p0);                    // columns of this tile that exist
+    const int lane = threadIdx.x % REC_LANES, col = (threadIdx.x / REC_LANES) * C;     // first of this group's columns in the tile
+    const int width = min(TILE, P - p0);                        // columns of this tile that exist
     const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), skip = __ldg(d_skip + h);
     const bool vec_x = vec && (width & 3) == 0;
 
@@ -278,7 +279,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         const float* row = xbc + (size_t)(first + c0) * xbc_cols;
         rec_stage(base, NP, row + inner + g * N, xbc_cols, count, N, vec);
         rec_stage(base + chunk * NP, NP, row + inner + groups * N + g * N, xbc_cols, count, N, vec);
-        rec_stage(base + 2 * chunk * NP, REC_COLS, row + h * P + p0, xbc_cols, count, width, vec_x);
+        rec_stage(base + 2 * chunk * NP, TILE, row + h * P + p0, xbc_cols, count, width, vec_x);
         rec_commit();
     };
     auto raw_step = [&](int c0) {                                // this thread's token of the chunk: the raw step size
@@ -286,16 +287,17 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     };
     auto put_scalars = [&](float* base, float raw) {
         const float dt = rec_softplus(raw + bias);
-        base[2 * chunk * NP + chunk * REC_COLS + threadIdx.x] = expf(neg_a * dt);
-        base[2 * chunk * NP + chunk * REC_COLS + chunk + threadIdx.x] = dt;
+        base[2 * chunk * NP + chunk * TILE + threadIdx.x] = expf(neg_a * dt);
+        base[2 * chunk * NP + chunk * TILE + chunk + threadIdx.x] = dt;
     };
 
     for (int e = threadIdx.x; e < 2 * buffer_floats; e += blockDim.x) rec_shared[e] = 0.0f;
     __syncthreads();
     stage(0, rec_shared);
-    float* S = state + (((size_t)slots[b] * heads + h) * P + (live ? p : 0)) * N;
-    float s[K];
-    rec_load_column<K>(s, S, lane, N, live);
+    float* S = state + (((size_t)slots[b] * heads + h) * P + p0 + col) * N;          // column c of the group lies c * N further
+    float s[C][K];
+#pragma unroll
+    for (int c = 0; c < C; ++c) rec_load_column<K>(s[c], S + (size_t)(p0 + col + c < P ? c : 0) * N, lane, N, p0 + col + c < P);
     if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_step(0));
     int it = 0;
     for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
@@ -315,51 +317,90 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         const float* Bs = cur;
         const float* Cs = cur + chunk * NP;
         const float* xs = cur + 2 * chunk * NP;
-        const float* decay = xs + chunk * REC_COLS;
+        const float* decay = xs + chunk * TILE;
         const float* step = decay + chunk;
         for (int k = 0; k < count; ++k) {
-            const float a = decay[k], x = live ? xs[k * REC_COLS + col] : 0.0f;
-            const float dx = step[k] * x;
+            const float a = decay[k], dt = step[k];
             float bv[K], cv[K];                                  // all of the token's loads are asked for before the arithmetic
             rec_load_vector<K>(bv, Bs + k * NP, lane);
             rec_load_vector<K>(cv, Cs + k * NP, lane);
-            float part0 = 0.0f, part1 = 0.0f;                    // two chains, so that neighbouring rows do not wait for each other
+            float x[C], part[C];
 #pragma unroll
-            for (int i = 0; i < K; i += 2) {
-                s[i] = fmaf(dx, bv[i], a * s[i]);
-                part0 = fmaf(s[i], cv[i], part0);
-                s[i + 1] = fmaf(dx, bv[i + 1], a * s[i + 1]);
-                part1 = fmaf(s[i + 1], cv[i + 1], part1);
+            for (int c = 0; c < C; ++c) {
+                x[c] = p0 + col + c < P ? xs[k * TILE + col + c] : 0.0f;
+                const float dx = dt * x[c];
+                float part0 = 0.0f, part1 = 0.0f;                // two chains, so that neighbouring rows do not wait for each other
+#pragma unroll
+                for (int i = 0; i < K; i += 2) {
+                    s[c][i] = fmaf(dx, bv[i], a * s[c][i]);
+                    part0 = fmaf(s[c][i], cv[i], part0);
+                    s[c][i + 1] = fmaf(dx, bv[i + 1], a * s[c][i + 1]);
+                    part1 = fmaf(s[c][i + 1], cv[i + 1], part1);
+                }
+                part[c] = part0 + part1;
             }
-            const float part = rec_group_sum(part0 + part1);
-            if (lane == 0 && live) y[(size_t)(first + c0 + k) * inner + h * P + p] = fmaf(skip, x, part);
+#pragma unroll
+            for (int o = REC_LANES / 2; o > 0; o >>= 1) {        // the columns' sums over the lane group, side by side
+#pragma unroll
+                for (int c = 0; c < C; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], o);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                    if (p0 + col + c < P) y[(size_t)(first + c0 + k) * inner + h * P + p0 + col + c] = fmaf(skip, x[c], part[c]);
+            }
         }
         if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
         __syncthreads();                                         // this buffer may be filled again; the next one's scalars are written
     }
-    if (live) rec_store_column<K>(s, S, lane, N);
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+        if (p0 + col + c < P) rec_store_column<K>(s[c], S + (size_t)c * N, lane, N);
 }
 
 // Tokens staged at a time: 16 where two buffers of them fit the default 48 KB of shared memory, else 8.
 static int rec_padded(int rows) { return rows <= 8 * REC_LANES ? 8 * REC_LANES : rows <= 16 * REC_LANES ? 16 * REC_LANES : 32 * REC_LANES; }
 static int rec_chunk(int rows) { return rows <= 128 ? REC_CHUNK : REC_CHUNK / 2; }
-static size_t rec_shared_bytes(int rows, int chunk) { return (size_t)2 * (2 * chunk * rec_padded(rows) + chunk * REC_COLS + 2 * chunk) * sizeof(float); }
+static size_t rec_shared_bytes(int rows, int chunk, int tile) { return (size_t)2 * (2 * chunk * rec_padded(rows) + chunk * tile + 2 * chunk) * sizeof(float); }
+
+constexpr int REC_WIDE_GROUPS = 16, REC_WIDE_COLS = 4;      // the form for grids that fill the GPU: 16 lane groups of 4 columns each
+
+// Whether the grid of the (32, 1) form would fill the GPU more than twice over, so that the (16, 4) form pays
+// (mode 0; 1 and 2 force the one or the other, for tests).  The wide form holds four columns of up to 128 rows.
+static bool rec_wide(int mode, long long ctas, int rows) {
+    if (rows > 16 * REC_LANES) return false;
+    if (mode) return mode == 2;
+    static int sms = 0;
+    if (!sms) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return ctas >= 2LL * sms;
+}
 static bool rec_aligned(const void* p, int a, int b, int c, int d) { return (((uintptr_t)p & 15) == 0) && !((a | b | c | d) & 3); }
 
 extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
                               int dt_col, const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
-                              const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups,
+                              const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups, int mode,
                               cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if (N <= 0 || N > REC_MAX_ROWS || P <= 0 || groups <= 0 || heads % groups || sequences > 65535) return (int)cudaErrorInvalidValue;
-    const dim3 grid(heads, sequences, (P + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
     const int chunk = rec_chunk(N);
-    const size_t shared = rec_shared_bytes(N, chunk);
     const int vec = rec_aligned(xbc, xbc_cols, N, P, 0) ? 1 : 0;          // every row piece starts on 16 bytes
-#define TT_SCAN(K) tt_launch_pdl(mamba2_scan_kernel<K>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups, chunk, vec)
-    if (N <= 8 * REC_LANES) TT_SCAN(8);
-    else if (N <= 16 * REC_LANES) TT_SCAN(16);
-    else TT_SCAN(32);
+    const bool wide = rec_wide(mode, (long long)heads * sequences * ((P + REC_COLS - 1) / REC_COLS), N);
+    const int tile = wide ? REC_WIDE_GROUPS * REC_WIDE_COLS : REC_COLS;
+    const dim3 grid(heads, sequences, (P + tile - 1) / tile), block((wide ? REC_WIDE_GROUPS : REC_COLS) * REC_LANES);
+    const size_t shared = rec_shared_bytes(N, chunk, tile);
+#define TT_SCAN(K, G, C) tt_launch_pdl(mamba2_scan_kernel<K, G, C>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups, chunk, vec)
+    if (wide) {
+        if (N <= 8 * REC_LANES) TT_SCAN(8, REC_WIDE_GROUPS, REC_WIDE_COLS);
+        else TT_SCAN(16, REC_WIDE_GROUPS, REC_WIDE_COLS);
+    } else {
+        if (N <= 8 * REC_LANES) TT_SCAN(8, REC_COLS, 1);
+        else if (N <= 16 * REC_LANES) TT_SCAN(16, REC_COLS, 1);
+        else TT_SCAN(32, REC_COLS, 1);
+    }
 #undef TT_SCAN
     TT_LAUNCH_CHECK();
 }
@@ -372,8 +413,8 @@ extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj,
 // qkv: float32 [tokens][2 * qk_heads * D + heads * V] (q, k, v: the convolutions' output); b_raw and
 // a_raw: columns b_col + h and a_col + h of the projection's partial sums; state: [slots][heads][V][D].
 // ------------------------------------------------------------------------------------
-template <int K>
-__global__ void __launch_bounds__(REC_COLS* REC_LANES)
+template <int K, int G, int C>
+__global__ void __launch_bounds__(G* REC_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __restrict__ proj, int splits, size_t split_stride,
                   int cols, int b_col, int a_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                   float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slots,
@@ -381,19 +422,17 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ __align__(16) float rec_shared[];
-    // two buffers of: q [chunk][DP], k [chunk][DP], v [chunk][REC_COLS], decay [chunk], beta [chunk]; rows are padded to
-    // DP = K * REC_LANES numbers and the padding is zero
-    constexpr int DP = K * REC_LANES;
-    const int buffer_floats = 2 * chunk * DP + chunk * REC_COLS + 2 * chunk;
-    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * REC_COLS;
+    // two buffers of: q [chunk][DP], k [chunk][DP], v [chunk][TILE], decay [chunk], beta [chunk]; rows are padded to
+    // DP = K * REC_LANES numbers and the padding is zero.  G lane groups of C neighbouring columns each, as in the kernel above.
+    constexpr int DP = K * REC_LANES, TILE = G * C;
+    const int buffer_floats = 2 * chunk * DP + chunk * TILE + 2 * chunk;
+    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * TILE;
     const int first = cu[b], n = cu[b + 1] - first;
     if (n <= 0) return;
     const int g = h / (heads / qk_heads);
-    const int lane = threadIdx.x % REC_LANES, col = threadIdx.x / REC_LANES;
+    const int lane = threadIdx.x % REC_LANES, col = (threadIdx.x / REC_LANES) * C;
     const int warp = threadIdx.x >> 5, wlane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int p = p0 + col;
-    const bool live = p < V;
-    const int width = min(REC_COLS, V - p0);
+    const int width = min(TILE, V - p0);
     const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), q_scale = rsqrtf((float)D);
     const int k_off = qk_heads * D, v_off = 2 * qk_heads * D;
     const bool vec_v = vec && (width & 3) == 0;
@@ -403,7 +442,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         const float* row = qkv + (size_t)(first + c0) * qkv_cols;
         rec_stage(base, DP, row + g * D, qkv_cols, count, D, vec);
         rec_stage(base + chunk * DP, DP, row + k_off + g * D, qkv_cols, count, D, vec);
-        rec_stage(base + 2 * chunk * DP, REC_COLS, row + v_off + h * V + p0, qkv_cols, count, width, vec_v);
+        rec_stage(base + 2 * chunk * DP, TILE, row + v_off + h * V + p0, qkv_cols, count, width, vec_v);
         rec_commit();
     };
     auto raw_pair = [&](int c0) {                                // this thread's token of the chunk: raw write strength, raw decay input
@@ -411,16 +450,17 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         return make_float2(rec_sum_slices(row + b_col + h, splits, split_stride), rec_sum_slices(row + a_col + h, splits, split_stride));
     };
     auto put_scalars = [&](float* base, float2 raw) {
-        base[2 * chunk * DP + chunk * REC_COLS + threadIdx.x] = expf(neg_a * rec_softplus(raw.y + bias));
-        base[2 * chunk * DP + chunk * REC_COLS + chunk + threadIdx.x] = 1.0f / (1.0f + expf(-raw.x));
+        base[2 * chunk * DP + chunk * TILE + threadIdx.x] = expf(neg_a * rec_softplus(raw.y + bias));
+        base[2 * chunk * DP + chunk * TILE + chunk + threadIdx.x] = 1.0f / (1.0f + expf(-raw.x));
     };
 
     for (int e = threadIdx.x; e < 2 * buffer_floats; e += blockDim.x) rec_shared[e] = 0.0f;
     __syncthreads();
     stage(0, rec_shared);
-    float* S = state + (((size_t)slots[b] * heads + h) * V + (live ? p : 0)) * D;
-    float s[K];
-    rec_load_column<K>(s, S, lane, D, live);
+    float* S = state + (((size_t)slots[b] * heads + h) * V + p0 + col) * D;
+    float s[C][K];
+#pragma unroll
+    for (int c = 0; c < C; ++c) rec_load_column<K>(s[c], S + (size_t)(p0 + col + c < V ? c : 0) * D, lane, D, p0 + col + c < V);
     if (threadIdx.x < min(chunk, n)) put_scalars(rec_shared, raw_pair(0));
     int it = 0;
     for (int c0 = 0; c0 < n; c0 += chunk, ++it) {
@@ -449,53 +489,84 @@ delta_scan_kernel(const float* __restrict__ qkv, int qkv_cols, const float* __re
         }
         __syncthreads();
         const float* vs = cur + 2 * chunk * DP;
-        const float* decay = vs + chunk * REC_COLS;
+        const float* decay = vs + chunk * TILE;
         const float* beta = decay + chunk;
         for (int k = 0; k < count; ++k) {
-            const float a = decay[k];
+            const float a = decay[k], write = beta[k];
             float kv[K], qv[K];                                  // all of the token's loads are asked for before the arithmetic
             rec_load_vector<K>(kv, ks + k * DP, lane);
             rec_load_vector<K>(qv, qs + k * DP, lane);
-            float part0 = 0.0f, part1 = 0.0f;
+            float part[C];
 #pragma unroll
-            for (int i = 0; i < K; i += 2) {
-                s[i] *= a;
-                part0 = fmaf(s[i], kv[i], part0);
-                s[i + 1] *= a;
-                part1 = fmaf(s[i + 1], kv[i + 1], part1);
-            }
-            const float u = beta[k] * ((live ? vs[k * REC_COLS + col] : 0.0f) - rec_group_sum(part0 + part1));
-            part0 = 0.0f, part1 = 0.0f;
+            for (int c = 0; c < C; ++c) {
+                float part0 = 0.0f, part1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < K; i += 2) {
-                s[i] = fmaf(kv[i], u, s[i]);
-                part0 = fmaf(s[i], qv[i], part0);
-                s[i + 1] = fmaf(kv[i + 1], u, s[i + 1]);
-                part1 = fmaf(s[i + 1], qv[i + 1], part1);
+                for (int i = 0; i < K; i += 2) {
+                    s[c][i] *= a;
+                    part0 = fmaf(s[c][i], kv[i], part0);
+                    s[c][i + 1] *= a;
+                    part1 = fmaf(s[c][i + 1], kv[i + 1], part1);
+                }
+                part[c] = part0 + part1;
             }
-            const float part = rec_group_sum(part0 + part1);
-            if (lane == 0 && live) o[(size_t)(first + c0 + k) * (heads * V) + h * V + p] = part;
+#pragma unroll
+            for (int o2 = REC_LANES / 2; o2 > 0; o2 >>= 1) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], o2);
+            }
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const float u = write * ((p0 + col + c < V ? vs[k * TILE + col + c] : 0.0f) - part[c]);
+                float part0 = 0.0f, part1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < K; i += 2) {
+                    s[c][i] = fmaf(kv[i], u, s[c][i]);
+                    part0 = fmaf(s[c][i], qv[i], part0);
+                    s[c][i + 1] = fmaf(kv[i + 1], u, s[c][i + 1]);
+                    part1 = fmaf(s[c][i + 1], qv[i + 1], part1);
+                }
+                part[c] = part0 + part1;
+            }
+#pragma unroll
+            for (int o2 = REC_LANES / 2; o2 > 0; o2 >>= 1) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], o2);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                    if (p0 + col + c < V) o[(size_t)(first + c0 + k) * (heads * V) + h * V + p0 + col + c] = part[c];
+            }
         }
         if (count_next > 0 && threadIdx.x < count_next) put_scalars(nxt, raw_next);
         __syncthreads();
     }
-    if (live) rec_store_column<K>(s, S, lane, D);
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+        if (p0 + col + c < V) rec_store_column<K>(s[c], S + (size_t)c * D, lane, D);
 }
 
 extern "C" int tt_delta_scan(const float* qkv, int qkv_cols, const float* proj, int splits, long long split_stride, int cols,
                              int b_col, int a_col, const float* dt_bias, const float* a_log, float* state, float* o,
-                             const int* cu, const int* slots, int sequences, int heads, int qk_heads, int D, int V,
+                             const int* cu, const int* slots, int sequences, int heads, int qk_heads, int D, int V, int mode,
                              cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if (D <= 0 || D > REC_MAX_ROWS || V <= 0 || qk_heads <= 0 || heads % qk_heads || sequences > 65535) return (int)cudaErrorInvalidValue;
-    const dim3 grid(heads, sequences, (V + REC_COLS - 1) / REC_COLS), block(REC_COLS * REC_LANES);
     const int chunk = rec_chunk(D);
-    const size_t shared = rec_shared_bytes(D, chunk);
     const int vec = rec_aligned(qkv, qkv_cols, D, V, 0) ? 1 : 0;
-#define TT_SCAN(K) tt_launch_pdl(delta_scan_kernel<K>, grid, block, shared, stream, qkv, qkv_cols, proj, splits, (size_t)split_stride, cols, b_col, a_col, dt_bias, a_log, state, o, cu, slots, heads, qk_heads, D, V, chunk, vec)
-    if (D <= 8 * REC_LANES) TT_SCAN(8);
-    else if (D <= 16 * REC_LANES) TT_SCAN(16);
-    else TT_SCAN(32);
+    const bool wide = rec_wide(mode, (long long)heads * sequences * ((V + REC_COLS - 1) / REC_COLS), D);
+    const int tile = wide ? REC_WIDE_GROUPS * REC_WIDE_COLS : REC_COLS;
+    const dim3 grid(heads, sequences, (V + tile - 1) / tile), block((wide ? REC_WIDE_GROUPS : REC_COLS) * REC_LANES);
+    const size_t shared = rec_shared_bytes(D, chunk, tile);
+#define TT_SCAN(K, G, C) tt_launch_pdl(delta_scan_kernel<K, G, C>, grid, block, shared, stream, qkv, qkv_cols, proj, splits, (size_t)split_stride, cols, b_col, a_col, dt_bias, a_log, state, o, cu, slots, heads, qk_heads, D, V, chunk, vec)
+    if (wide) {
+        if (D <= 8 * REC_LANES) TT_SCAN(8, REC_WIDE_GROUPS, REC_WIDE_COLS);
+        else TT_SCAN(16, REC_WIDE_GROUPS, REC_WIDE_COLS);
+    } else {
+        if (D <= 8 * REC_LANES) TT_SCAN(8, REC_COLS, 1);
+        else if (D <= 16 * REC_LANES) TT_SCAN(16, REC_COLS, 1);
+        else TT_SCAN(32, REC_COLS, 1);
+    }
 #undef TT_SCAN
     TT_LAUNCH_CHECK();
 }

@@ -514,12 +514,17 @@ def causal_conv(proj: torch.Tensor, col_off: int, channels: int, weight: torch.T
               _stream()), "causal_conv", (0 if one_token_each else 1) + (1 if taps > 1 or one_token_each else 0))
 
 
+SCAN_FORMS = {"auto": 0, "narrow": 1, "wide": 2}
+
+
 def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
                 state: torch.Tensor, y: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, heads: int,
-                head_dim: int, state_size: int, groups: int) -> None:
+                head_dim: int, state_size: int, groups: int, form: str = "auto") -> None:
     """The Mamba-2 recurrence over each sequence's tokens.  ``xbc`` float32 [tokens, inner + 2 * groups * state_size]
     holds x, B and C; column ``dt_col + h`` of ``proj`` the raw step size of head h; ``state`` float32
-    [slots, heads, head_dim, state_size]; ``y`` float32 [tokens, inner] receives S^T C + D x."""
+    [slots, heads, head_dim, state_size]; ``y`` float32 [tokens, inner] receives S^T C + D x.  ``form``: ``auto`` takes
+    the form with one column per lane group unless that grid would fill the GPU more than twice over, then the one with
+    four (``narrow`` / ``wide`` force one; both give the same bits, a column's arithmetic is the same)."""
     inner = heads * head_dim
     for t, name in ((xbc, "x/B/C"), (dt_bias, "dt_bias"), (a_log, "A_log"), (d_skip, "D"), (state, "recurrent state"), (y, "recurrence output")):
         _need(t, torch.float32, name)
@@ -527,18 +532,19 @@ def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: tor
         raise KernelError("mamba2_scan: shapes do not fit the sizes")
     p, splits, stride, cols = _projection(proj)
     fn = _fn("recurrent", "tt_mamba2_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(xbc), xbc.shape[1], p, splits, stride, cols, dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(y),
-              _ptr(cu), _ptr(slots), sequences, heads, head_dim, state_size, groups, _stream()), "mamba2_scan")
+              _ptr(cu), _ptr(slots), sequences, heads, head_dim, state_size, groups, SCAN_FORMS[form], _stream()), "mamba2_scan")
 
 
 def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
                state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, heads: int, qk_heads: int,
-               key_dim: int, value_dim: int) -> None:
+               key_dim: int, value_dim: int, form: str = "auto") -> None:
     """The gated delta rule over each sequence's tokens.  ``qkv`` float32 [tokens, 2 * qk_heads * key_dim + heads *
     value_dim] holds q, k, v (q and k are made unit vectors here, q also times key_dim^-1/2); columns ``b_col + h`` and
     ``a_col + h`` of ``proj`` the raw write strength and decay input of head h; ``state`` float32
-    [slots, heads, value_dim, key_dim]; ``out`` float32 [tokens, heads * value_dim] receives S^T q."""
+    [slots, heads, value_dim, key_dim]; ``out`` float32 [tokens, heads * value_dim] receives S^T q.  ``form``: as for
+    :func:`mamba2_scan`."""
     for t, name in ((qkv, "q/k/v"), (dt_bias, "dt_bias"), (a_log, "A_log"), (state, "recurrent state"), (out, "recurrence output")):
         _need(t, torch.float32, name)
     if (qkv.shape[1] != 2 * qk_heads * key_dim + heads * value_dim or tuple(state.shape[1:]) != (heads, value_dim, key_dim)
@@ -546,9 +552,9 @@ def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, dt
         raise KernelError("delta_scan: shapes do not fit the sizes")
     p, splits, stride, cols = _projection(proj)
     fn = _fn("recurrent", "tt_delta_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], p, splits, stride, cols, b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(out),
-              _ptr(cu), _ptr(slots), sequences, heads, qk_heads, key_dim, value_dim, _stream()), "delta_scan")
+              _ptr(cu), _ptr(slots), sequences, heads, qk_heads, key_dim, value_dim, SCAN_FORMS[form], _stream()), "delta_scan")
 
 
 def gated_group_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, gate_first: bool,
