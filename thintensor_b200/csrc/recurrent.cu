@@ -15,7 +15,9 @@
 // in registers (four neighbouring rows at a time, so that a token's vectors come out of shared memory, and the
 // state out of global memory, in 16-byte pieces that the group's lanes read side by side).  Row products with the token's vectors (read from shared memory, where a chunk of tokens
 // is staged) are summed inside the group with shuffles.  Columns are independent, so a CTA takes
-// REC_COLS of them for one (sequence, head) and the grid is heads x sequences x column tiles.
+// REC_COLS of them for one (sequence, head) and the grid is heads x sequences x column tiles.  When that
+// grid would fill the GPU more than twice over, a lane group owns four neighbouring columns instead and
+// a CTA 64 of them (see the kernels' template parameters).
 #include "common.cuh"
 
 constexpr int REC_LANES = 8;        // lanes that share one state column (measured on a B200, 64 heads of 64 x 128: one sequence of 2,048
