@@ -73,8 +73,9 @@ def test_config_errors(change, needle):
 
 
 def test_registry():
-    assert supported_architectures() == ["Famalorn", "LlamaForCausalLM"]
+    assert supported_architectures() == ["Famalorn", "LlamaForCausalLM", "Neruzen"]
     assert resolve_architecture({"architecture": "Famalorn"}).name == "Famalorn"
+    assert resolve_architecture({"architecture": "Neruzen"}).name == "Neruzen"
     assert resolve_architecture({"architectures": ["LlamaForCausalLM"]}).name == "LlamaForCausalLM"
     assert resolve_architecture({"model_type": "llama"}).name == "LlamaForCausalLM"
     assert resolve_architecture({"model_type": "Tiny-Llama"}).name == "LlamaForCausalLM"

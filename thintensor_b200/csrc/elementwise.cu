@@ -716,3 +716,103 @@ extern "C" int tt_copy_int32(int* dst, const int* src, int n, const int* extra, 
     tt_launch_pdl(copy_int32_kernel, dim3((n + 1 + 127) / 128), dim3(128), 0, stream, dst, src, n, extra);
     TT_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------
+// Embedding with a hashed row for the pair (previous token, token):
+//   residual[t] = table[token] * scale + pair_table[(prev * mul_prev + token * mul_cur) mod buckets]
+// and row `buckets` (the last) of pair_table for a sequence's first token.  The previous token of a
+// step's first token comes from the sequence's state, one int32 per slot that holds the last token
+// plus one (zero: the sequence has no token yet); the block of a sequence's first token of the step
+// reads it and then moves it on to the step's last token, so nobody else touches it.
+// ------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_pair_gather_kernel(const TW* __restrict__ table, const TW* __restrict__ pair_table,
+                                         const int* __restrict__ tokens, const int* __restrict__ cu,
+                                         const int* __restrict__ slots, int sequences, int* __restrict__ last_token,
+                                         float* __restrict__ residual, int hidden, int vocab, int buckets, long long mul_prev,
+                                         long long mul_cur, float scale, unsigned* status) {
+    tt_pdl_wait();                      // the first kernel of a step: see embed_gather_kernel
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int id = tokens[t];
+    int prev_plus_one;
+    if (t == cu[b]) {
+        int* st = last_token + slots[b];
+        prev_plus_one = *st;
+        __syncthreads();                // every thread has read the state before one of them moves it on
+        if (threadIdx.x == 0) *st = tokens[cu[b + 1] - 1] + 1;
+    } else {
+        prev_plus_one = tokens[t - 1] + 1;
+    }
+    float* out = residual + (size_t)t * hidden;
+    if (id < 0 || id >= vocab || prev_plus_one < 0 || prev_plus_one > vocab) {
+        if (threadIdx.x == 0) atomicOr(status, TT_STATUS_BAD_TOKEN);
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = 0.0f;
+        return;
+    }
+    const long long pair = prev_plus_one == 0 ? (long long)buckets
+                                              : ((long long)(prev_plus_one - 1) * mul_prev + (long long)id * mul_cur) % buckets;
+    const TW* row = table + (size_t)id * hidden;
+    const TW* extra = pair_table + (size_t)pair * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = tt_to_float(row[j]) * scale + tt_to_float(extra[j]);
+}
+
+extern "C" int tt_embed_pair_gather(const void* table, const void* pair_table, int table_dtype, const int* tokens, const int* cu,
+                                    const int* slots, int sequences, int* last_token, float* residual, int n_tokens, int hidden,
+                                    int vocab, int buckets, long long mul_prev, long long mul_cur, float scale, unsigned* status,
+                                    cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return (int)cudaErrorInvalidValue;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == TT_F32)
+        tt_launch_pdl(embed_pair_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, (const float*)pair_table, tokens, cu, slots, sequences, last_token, residual, hidden, vocab, buckets, mul_prev, mul_cur, scale, status);
+    else
+        tt_launch_pdl(embed_pair_gather_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pair_table, tokens, cu, slots, sequences, last_token, residual, hidden, vocab, buckets, mul_prev, mul_cur, scale, status);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Token shift: out[t] = x[t] + (x[t - 1] - x[t]) * mix, element by element, where x[t - 1] of a step's
+// first token is the sequence's state (float32 [slots][hidden], zero for a new sequence).  The block of a
+// sequence's first token of the step reads the state and moves it on to the step's last x, element by
+// element in the same thread.
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mix, float* __restrict__ state,
+                                   T* __restrict__ out, const int* __restrict__ cu, const int* __restrict__ slots, int sequences,
+                                   int hidden) {
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int first = cu[b], last = cu[b + 1] - 1;
+    tt_pdl_wait();
+    const T* cur = x + (size_t)t * hidden;
+    T* o = out + (size_t)t * hidden;
+    if (t == first) {
+        float* st = state + (size_t)slots[b] * hidden;
+        const T* tail = x + (size_t)last * hidden;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+            const float before = st[j], now = tt_to_float(cur[j]);
+            st[j] = tt_to_float(tail[j]);
+            o[j] = tt_from_float<T>(fmaf(before - now, __ldg(mix + j), now));
+        }
+    } else {
+        const T* prev = cur - hidden;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+            const float before = tt_to_float(prev[j]), now = tt_to_float(cur[j]);
+            o[j] = tt_from_float<T>(fmaf(before - now, __ldg(mix + j), now));
+        }
+    }
+}
+
+extern "C" int tt_token_shift(const void* x, int dtype, const float* mix, float* state, void* out, const int* cu, const int* slots,
+                              int sequences, int n_tokens, int hidden, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == TT_F32)
+        tt_launch_pdl(token_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)x, mix, state, (float*)out, cu, slots, sequences, hidden);
+    else
+        tt_launch_pdl(token_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)x, mix, state, (__nv_bfloat16*)out, cu, slots, sequences, hidden);
+    TT_LAUNCH_CHECK();
+}

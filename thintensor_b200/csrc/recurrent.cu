@@ -69,6 +69,8 @@ __device__ __forceinline__ void rec_stage(float* dst, int dst_stride, const floa
 }
 
 __device__ __forceinline__ float rec_silu(float x) { return x / (1.0f + expf(-x)); }
+// the gate of a normed read-out: 0 silu, 1 sigmoid
+__device__ __forceinline__ float rec_gate(float x, int kind) { return kind == 1 ? 1.0f / (1.0f + expf(-x)) : rec_silu(x); }
 __device__ __forceinline__ float rec_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
 // the state row that register i of lane `lane` holds
@@ -258,7 +260,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
                    int cols, int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                    const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
                    const int* __restrict__ cu, const int* __restrict__ slots, int heads, int P, int N, int groups, int chunk,
-                   int vec) {
+                   int vec, const float* __restrict__ fixed_decay) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ __align__(16) float rec_shared[];
@@ -273,7 +275,10 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
     const int inner = heads * P;
     const int lane = threadIdx.x % REC_LANES, col = (threadIdx.x / REC_LANES) * C;     // first of this group's columns in the tile
     const int width = min(TILE, P - p0);                        // columns of this tile that exist
-    const float neg_a = -expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), skip = __ldg(d_skip + h);
+    // fixed_decay: the head's decay is a constant and every step size is one (S = decay * S + B x^T, y = S^T C)
+    const float fixed = fixed_decay ? __ldg(fixed_decay + h) : 0.0f;
+    const float neg_a = fixed_decay ? 0.0f : -expf(__ldg(a_log + h)), bias = fixed_decay ? 0.0f : __ldg(dt_bias + h);
+    const float skip = fixed_decay ? 0.0f : __ldg(d_skip + h);
     const bool vec_x = vec && (width & 3) == 0;
 
     auto stage = [&](int c0, float* base) {                      // asynchronous: B, C and x of tokens c0 .. of this sequence
@@ -285,11 +290,12 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int xbc_cols, const float* __r
         rec_commit();
     };
     auto raw_step = [&](int c0) {                                // this thread's token of the chunk: the raw step size
+        if (fixed_decay) return 0.0f;
         return rec_sum_slices(proj + (size_t)(first + c0 + threadIdx.x) * cols + dt_col + h, splits, split_stride);
     };
     auto put_scalars = [&](float* base, float raw) {
-        const float dt = rec_softplus(raw + bias);
-        base[2 * chunk * NP + chunk * TILE + threadIdx.x] = expf(neg_a * dt);
+        const float dt = fixed_decay ? 1.0f : rec_softplus(raw + bias);
+        base[2 * chunk * NP + chunk * TILE + threadIdx.x] = fixed_decay ? fixed : expf(neg_a * dt);
         base[2 * chunk * NP + chunk * TILE + chunk + threadIdx.x] = dt;
     };
 
@@ -382,10 +388,10 @@ static bool rec_wide(int mode, long long ctas, int rows) {
 }
 static bool rec_aligned(const void* p, int a, int b, int c, int d) { return (((uintptr_t)p & 15) == 0) && !((a | b | c | d) & 3); }
 
-extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
+static int mamba2_scan_launch(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
                               int dt_col, const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
                               const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups, int mode,
-                              cudaStream_t stream) {
+                              const float* fixed_decay, cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if (N <= 0 || N > REC_MAX_ROWS || P <= 0 || groups <= 0 || heads % groups || sequences > 65535) return (int)cudaErrorInvalidValue;
     const int chunk = rec_chunk(N);
@@ -394,7 +400,7 @@ extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj,
     const int tile = wide ? REC_WIDE_GROUPS * REC_WIDE_COLS : REC_COLS;
     const dim3 grid(heads, sequences, (P + tile - 1) / tile), block((wide ? REC_WIDE_GROUPS : REC_COLS) * REC_LANES);
     const size_t shared = rec_shared_bytes(N, chunk, tile);
-#define TT_SCAN(K, G, C) tt_launch_pdl(mamba2_scan_kernel<K, G, C>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups, chunk, vec)
+#define TT_SCAN(K, G, C) tt_launch_pdl(mamba2_scan_kernel<K, G, C>, grid, block, shared, stream, xbc, xbc_cols, proj, splits, (size_t)split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots, heads, P, N, groups, chunk, vec, fixed_decay)
     if (wide) {
         if (N <= 8 * REC_LANES) TT_SCAN(8, REC_WIDE_GROUPS, REC_WIDE_COLS);
         else TT_SCAN(16, REC_WIDE_GROUPS, REC_WIDE_COLS);
@@ -404,6 +410,79 @@ extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj,
         else TT_SCAN(32, REC_COLS, 1);
     }
 #undef TT_SCAN
+    TT_LAUNCH_CHECK();
+}
+
+extern "C" int tt_mamba2_scan(const float* xbc, int xbc_cols, const float* proj, int splits, long long split_stride, int cols,
+                              int dt_col, const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
+                              const int* cu, const int* slots, int sequences, int heads, int P, int N, int groups, int mode,
+                              cudaStream_t stream) {
+    return mamba2_scan_launch(xbc, xbc_cols, proj, splits, split_stride, cols, dt_col, dt_bias, a_log, d_skip, state, y, cu, slots,
+                              sequences, heads, P, N, groups, mode, nullptr, stream);
+}
+
+// ------------------------------------------------------------------------------------
+// Linear attention with a fixed decay per head: S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, S [D x V] per head.
+// It is the recurrence above with a constant decay, step size one, B = k, C = q, x = v and no skip, a group per head;
+// vkq: float32 [tokens][heads * V + 2 * heads * D] (v, then k, then q: what tt_linear_attention_prepare writes);
+// state: [slots][heads][V][D].
+// ------------------------------------------------------------------------------------
+extern "C" int tt_decay_scan(const float* vkq, int vkq_cols, const float* decay, float* state, float* out, const int* cu,
+                             const int* slots, int sequences, int heads, int V, int D, int mode, cudaStream_t stream) {
+    if (!decay) return (int)cudaErrorInvalidValue;
+    return mamba2_scan_launch(vkq, vkq_cols, nullptr, 0, 0, 0, 0, nullptr, nullptr, nullptr, state, out, cu, slots, sequences, heads, V, D,
+                              heads, mode, decay, stream);
+}
+
+// q, k and v of a linear attention from the partial sums of its input projection (columns [q | k | v | ...], q and k
+// heads x D, v heads x V), as the scan reads them: [v | k | q].  activation != 0: silu on all three.  rotary_dim > 0:
+// the first rotary_dim numbers of each head of q and k are rotated by the token's position (number i pairs with
+// i + rotary_dim / 2, angle = position * inv_freq[i], float32).  k is multiplied by k_scale after the rotation.
+__global__ void linear_attention_prepare_kernel(const float* __restrict__ proj, int splits, size_t split_stride, int cols, int heads,
+                                                int D, int V, int activation, const float* __restrict__ inv_freq, int rotary_dim,
+                                                float k_scale, float* __restrict__ vkq, const int* __restrict__ cu,
+                                                const int* __restrict__ len_before, int sequences) {
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x;
+    int pos = 0;
+    if (rotary_dim > 0) {
+        const int b = tt_find_sequence(cu, sequences, t);
+        pos = len_before[b] + (t - cu[b]);
+    }
+    tt_pdl_wait();
+    const int qk = heads * D, hv = heads * V;
+    const float* row = proj + (size_t)t * cols;
+    float* out = vkq + (size_t)t * (hv + 2 * qk);
+    const int half = rotary_dim >> 1;
+    for (int j = threadIdx.x; j < 2 * qk + hv; j += blockDim.x) {
+        float x = rec_sum_slices(row + j, splits, split_stride);
+        if (activation) x = rec_silu(x);
+        if (j >= 2 * qk) {                                       // v
+            out[j - 2 * qk] = x;
+            continue;
+        }
+        const bool is_k = j >= qk;
+        const int i = (is_k ? j - qk : j) % D;
+        if (i < rotary_dim) {
+            const int pair = i < half ? j + half : j - half;
+            float other = rec_sum_slices(row + pair, splits, split_stride);
+            if (activation) other = rec_silu(other);
+            float sn, cs;
+            sincosf((float)pos * __ldg(inv_freq + (i < half ? i : i - half)), &sn, &cs);
+            x = i < half ? x * cs - other * sn : x * cs + other * sn;
+        }
+        if (is_k) out[hv + (j - qk)] = x * k_scale;
+        else out[hv + qk + j] = x;
+    }
+}
+
+extern "C" int tt_linear_attention_prepare(const float* proj, int splits, long long split_stride, int cols, int heads, int D, int V,
+                                           int activation, const float* inv_freq, int rotary_dim, float k_scale, float* vkq,
+                                           const int* cu, const int* len_before, int sequences, int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || 2 * heads * D + heads * V > cols) return (int)cudaErrorInvalidValue;
+    tt_launch_pdl(linear_attention_prepare_kernel, dim3(n_tokens), dim3(256), 0, stream, proj, splits, (size_t)split_stride, cols, heads, D,
+                  V, activation, inv_freq, rotary_dim, k_scale, vkq, cu, len_before, sequences);
     TT_LAUNCH_CHECK();
 }
 
@@ -585,7 +664,7 @@ template <typename TOut>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, int width, int group, const float* __restrict__ proj,
                                         int splits, size_t split_stride, int cols, int gate_col,
                                         const float* __restrict__ weight, int weight_len, float eps, int gate_first,
-                                        TOut* __restrict__ out) {
+                                        TOut* __restrict__ out, int gate_kind) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     __shared__ float reduce[32];
@@ -596,13 +675,13 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int width, 
     float sumsq = 0.0f;
     for (int j = threadIdx.x; j < group; j += blockDim.x) {
         float v = yr[j];
-        if (gate_first) v *= rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+        if (gate_first) v *= rec_gate(rec_sum_slices(gr + j, splits, split_stride), gate_kind);
         sumsq += v * v;
     }
     const float r = rsqrtf(tt_block_sum(sumsq, reduce) / (float)group + eps);
     TOut* o = out + (size_t)t * width + (size_t)gi * group;
     for (int j = threadIdx.x; j < group; j += blockDim.x) {
-        const float gate = rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+        const float gate = rec_gate(rec_sum_slices(gr + j, splits, split_stride), gate_kind);
         const float w = __ldg(weight + (gi * group + j) % weight_len);
         const float v = gate_first ? yr[j] * gate * r * w : yr[j] * r * w * gate;
         o[j] = tt_from_float<TOut>(v);
@@ -617,7 +696,7 @@ template <typename TOut>
 __global__ void __launch_bounds__(1024)
 gated_group_norm_reg_kernel(const float* __restrict__ y, int width, int group, const float* __restrict__ proj, int splits,
                             size_t split_stride, int cols, int gate_col, const float* __restrict__ weight, int weight_len,
-                            float eps, int gate_first, TOut* __restrict__ out) {
+                            float eps, int gate_first, TOut* __restrict__ out, int gate_kind) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     __shared__ float reduce[32];
@@ -633,7 +712,7 @@ gated_group_norm_reg_kernel(const float* __restrict__ y, int width, int group, c
         v[e] = 0.0f;
         gate[e] = 0.0f;
         if (j < group) {
-            gate[e] = rec_silu(rec_sum_slices(gr + j, splits, split_stride));
+            gate[e] = rec_gate(rec_sum_slices(gr + j, splits, split_stride), gate_kind);
             v[e] = gate_first ? yr[j] * gate[e] : yr[j];
             sumsq = fmaf(v[e], v[e], sumsq);
         }
@@ -652,7 +731,7 @@ gated_group_norm_reg_kernel(const float* __restrict__ y, int width, int group, c
 
 extern "C" int tt_gated_group_norm(const float* y, int n_tokens, int width, int group, const float* proj, int splits,
                                    long long split_stride, int cols, int gate_col, const float* weight, int weight_len, float eps,
-                                   int gate_first, void* out, int out_dtype, cudaStream_t stream) {
+                                   int gate_first, void* out, int out_dtype, int gate_kind, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (group <= 0 || width % group || weight_len <= 0) return (int)cudaErrorInvalidValue;
     const long long blocks = (long long)n_tokens * (width / group);
@@ -661,16 +740,16 @@ extern "C" int tt_gated_group_norm(const float* y, int n_tokens, int width, int 
         int threads = (((group + 3) / 4 + 31) / 32) * 32;       // about four numbers a thread
         if (threads > 1024) threads = 1024;
         if (out_dtype == TT_F32)
-            tt_launch_pdl(gated_group_norm_reg_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out);
+            tt_launch_pdl(gated_group_norm_reg_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out, gate_kind);
         else
-            tt_launch_pdl(gated_group_norm_reg_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out);
+            tt_launch_pdl(gated_group_norm_reg_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out, gate_kind);
         TT_LAUNCH_CHECK();
     }
     const int threads = group >= 2048 ? 256 : (group >= 256 ? 128 : (group > 32 ? 64 : 32));
     if (out_dtype == TT_F32)
-        tt_launch_pdl(gated_group_norm_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out);
+        tt_launch_pdl(gated_group_norm_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (float*)out, gate_kind);
     else
-        tt_launch_pdl(gated_group_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out);
+        tt_launch_pdl(gated_group_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, y, width, group, proj, splits, (size_t)split_stride, cols, gate_col, weight, weight_len, eps, gate_first, (__nv_bfloat16*)out, gate_kind);
     TT_LAUNCH_CHECK();
 }
 

@@ -111,8 +111,9 @@ class DecoderModel:
         self.users: list[list[int]] = []
         for run in self.spec.schedule:
             mixers = self.layers[run.layer].mixers()
-            mine = list(range(len(kv), len(kv) + len(mixers)))
-            if run.cache_from is not None and len(self.users[run.cache_from]) != len(mixers):
+            own = list(self.layers[run.layer].state_needs())        # states of the arrangement itself: one more entry behind the mixers'
+            mine = list(range(len(kv), len(kv) + len(mixers) + (1 if own else 0)))
+            if run.cache_from is not None and len(self.layers[self.spec.schedule[run.cache_from].layer].mixers()) != len(mixers):
                 raise ValueError(f"a run of layer {run.layer} reads the cache of a run with another number of mixers")
             for i, mixer in enumerate(mixers):
                 need = mixer.cache_need()
@@ -120,7 +121,19 @@ class DecoderModel:
                 state.append(list(mixer.state_needs()))
                 # only keys are shared: a mixer without keys has nothing to read there, and states are always a run's own
                 source.append(None if run.cache_from is None or need is None else self.users[run.cache_from][i])
+            if own:
+                kv.append(None)
+                state.append(own)
+                source.append(None)
             self.users.append(mine)
+        # the embedding's states (the previous token, say) are the last entry
+        self.embedding_entry: int | None = None
+        own = list(self.embedding.part.state_needs())
+        if own:
+            self.embedding_entry = len(kv)
+            kv.append(None)
+            state.append(own)
+            source.append(None)
         return kv, state, source
 
     def new_cache(self, num_blocks: int, max_slots: int, device: torch.device | str | None = "default") -> SequenceCache:
@@ -137,7 +150,7 @@ class DecoderModel:
         if not self.bound:
             raise RuntimeError("the model has no weights yet")
         residual = ctx.scratch("model.residual", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
-        self.embedding.part.forward(ctx, ctx.tokens, residual)
+        self.embedding.part.forward(ctx, ctx.tokens, residual, None if self.embedding_entry is None else cache.run_state(self.embedding_entry))
         pending: Delta | None = None
         for index, run in enumerate(self.spec.schedule):
             users = self.users[index]

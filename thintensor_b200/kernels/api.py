@@ -166,6 +166,42 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tens
     _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(residual), n, hidden, table.shape[0], scale, _ptr(status), _stream()), "embed_gather")
 
 
+def embed_pair_gather(table: torch.Tensor, pair_table: torch.Tensor, tokens: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor,
+                      sequences: int, last_token: torch.Tensor, residual: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int,
+                      scale: float, status: torch.Tensor) -> None:
+    """residual[t] = table[tokens[t]] * scale + pair_table[(previous * mul_prev + tokens[t] * mul_cur) % buckets], and row
+    ``buckets`` of ``pair_table`` for a sequence's first token.  ``last_token`` (int32 ``[slots]``, last token plus one, zero for a
+    sequence without tokens) gives the token before the step's first one and is moved on to the step's last."""
+    _need(tokens, torch.int32, "tokens")
+    _need(residual, torch.float32, "residual")
+    _need(last_token, torch.int32, "the sequences' last tokens")
+    if not table.is_contiguous() or not pair_table.is_contiguous() or table.dtype != pair_table.dtype:
+        raise KernelError("embedding tables must be contiguous and of one dtype")
+    if pair_table.shape[0] != buckets + 1 or pair_table.shape[1] != table.shape[1]:
+        raise KernelError(f"the pair table must be [{buckets + 1}, {table.shape[1]}], got {tuple(pair_table.shape)}")
+    n, hidden = tokens.numel(), table.shape[1]
+    fn = _fn("elementwise", "tt_embed_pair_gather", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                     c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(table), _ptr(pair_table), dtype_code(table.dtype), _ptr(tokens), _ptr(cu), _ptr(slots), sequences, _ptr(last_token),
+              _ptr(residual), n, hidden, table.shape[0], buckets, mul_prev, mul_cur, scale, _ptr(status), _stream()), "embed_pair_gather")
+
+
+def token_shift(x: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor,
+                sequences: int) -> None:
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mix within each sequence; the row before a step's first one is ``state[slot]``
+    (float32 ``[slots, hidden]``, zero for a new sequence), which is moved on to the step's last row."""
+    _need(mix, torch.float32, "shift weights")
+    _need(state, torch.float32, "shift state")
+    if x.dtype != out.dtype or x.shape != out.shape or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("token_shift: input and output must be contiguous and alike")
+    tokens, hidden = x.shape
+    if mix.numel() != hidden or state.shape[1] != hidden:
+        raise KernelError("token_shift: weights or state do not fit the width")
+    fn = _fn("elementwise", "tt_token_shift", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(mix), _ptr(state), _ptr(out), _ptr(cu), _ptr(slots), sequences, tokens, hidden, _stream()),
+           "token_shift")
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: torch.Tensor | None = None, weight_offset: float = 0.0) -> None:
     """residual += sum(delta over its first axis); out = rmsnorm(residual) * weight.
@@ -557,11 +593,17 @@ def delta_scan(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, dt
               _ptr(cu), _ptr(slots), sequences, heads, qk_heads, key_dim, value_dim, SCAN_FORMS[form], _stream()), "delta_scan")
 
 
+NORM_GATES = {"silu": 0, "sigmoid": 1}
+
+
 def gated_group_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, gate_first: bool,
-                     out: torch.Tensor) -> None:
+                     out: torch.Tensor, gate: str = "silu") -> None:
     """Groups of ``group`` neighbouring columns of ``y`` (float32 [tokens, width]) divided by their root mean square,
     times ``weight`` (indexed by column modulo its length), with the gate silu(columns ``gate_col ..`` of ``proj``)
-    multiplied in before the norm (``gate_first``) or after it."""
+    multiplied in before the norm (``gate_first``) or after it; ``gate="sigmoid"`` takes the logistic function of the
+    columns instead of silu."""
+    if gate not in NORM_GATES:
+        raise KernelError(f"the gate of a normed read-out is one of {sorted(NORM_GATES)}, not {gate!r}")
     _need(y, torch.float32, "norm input")
     _need(weight, torch.float32, "norm weight")
     tokens, width = y.shape
@@ -571,9 +613,47 @@ def gated_group_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_col: 
     if gate_col + width > cols:
         raise KernelError("gated_group_norm: the gate lies outside the projection")
     fn = _fn("recurrent", "tt_gated_group_norm", [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
-                                                  c_float, c_int, c_void_p, c_int, c_void_p])
+                                                  c_float, c_int, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(y), tokens, width, group, p, splits, stride, cols, gate_col, _ptr(weight), weight.numel(), eps, 1 if gate_first else 0,
-              _ptr(out), dtype_code(out.dtype), _stream()), "gated_group_norm")
+              _ptr(out), dtype_code(out.dtype), NORM_GATES[gate], _stream()), "gated_group_norm")
+
+
+def linear_attention_prepare(proj: torch.Tensor, heads: int, key_dim: int, value_dim: int, activation: bool, inv_freq: torch.Tensor | None,
+                             rotary_dim: int, k_scale: float, vkq: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor,
+                             sequences: int, n_tokens: int) -> None:
+    """q, k and v of a linear attention from the partial sums of its input projection (columns ``[q | k | v | ...]``) as
+    :func:`decay_scan` reads them, ``vkq`` float32 ``[tokens, heads * value_dim + 2 * heads * key_dim]``: silu on all three
+    (``activation``), the first ``rotary_dim`` numbers of each head of q and k rotated by the position (halves paired), k times
+    ``k_scale``."""
+    _need(vkq, torch.float32, "v/k/q")
+    if tuple(vkq.shape) != (n_tokens, heads * value_dim + 2 * heads * key_dim):
+        raise KernelError("linear_attention_prepare: the output does not fit the sizes")
+    if rotary_dim:
+        _need(inv_freq, torch.float32, "inverse frequencies")
+        if inv_freq.numel() < rotary_dim // 2:
+            raise KernelError("linear_attention_prepare: too few inverse frequencies")
+    p, splits, stride, cols = _projection(proj)
+    fn = _fn("recurrent", "tt_linear_attention_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                                          c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(p, splits, stride, cols, heads, key_dim, value_dim, 1 if activation else 0, _ptr(inv_freq) if rotary_dim else c_void_p(0),
+              rotary_dim, k_scale, _ptr(vkq), _ptr(cu), _ptr(len_before), sequences, n_tokens, _stream()), "linear_attention_prepare")
+
+
+def decay_scan(vkq: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor,
+               sequences: int, heads: int, key_dim: int, value_dim: int, form: str = "auto") -> None:
+    """Linear attention with a fixed decay per head over each sequence's tokens: ``S = decay_h * S + k v^T``, ``o = S^T q``.
+    ``vkq`` float32 ``[tokens, heads * value_dim + 2 * heads * key_dim]`` (v, k, q); ``decay`` float32 ``[heads]``; ``state``
+    float32 ``[slots, heads, value_dim, key_dim]``; ``out`` float32 ``[tokens, heads * value_dim]``.  ``form``: as for
+    :func:`mamba2_scan`, whose kernel this runs with a constant decay and step size one."""
+    for t, name in ((vkq, "v/k/q"), (decay, "decay"), (state, "recurrent state"), (out, "recurrence output")):
+        _need(t, torch.float32, name)
+    if (vkq.shape[1] != heads * value_dim + 2 * heads * key_dim or tuple(state.shape[1:]) != (heads, value_dim, key_dim)
+            or out.shape[1] != heads * value_dim or decay.numel() != heads):
+        raise KernelError("decay_scan: shapes do not fit the sizes")
+    fn = _fn("recurrent", "tt_decay_scan", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_int, c_void_p])
+    _check(fn(_ptr(vkq), vkq.shape[1], _ptr(decay), _ptr(state), _ptr(out), _ptr(cu), _ptr(slots), sequences, heads, value_dim, key_dim,
+              SCAN_FORMS[form], _stream()), "decay_scan")
 
 
 def weighted_pair(a: torch.Tensor, wa: float, b: torch.Tensor, wb: float, out: torch.Tensor) -> None:
@@ -584,6 +664,109 @@ def weighted_pair(a: torch.Tensor, wa: float, b: torch.Tensor, wb: float, out: t
         raise KernelError("weighted_pair: shapes differ")
     fn = _fn("recurrent", "tt_weighted_pair", [c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float, c_void_p, c_longlong, c_void_p])
     _check(fn(_ptr(a), a.shape[0], a.stride(0), wa, _ptr(b), b.shape[0], b.stride(0), wb, _ptr(out), out.numel(), _stream()), "weighted_pair")
+
+
+# --------------------------------------------------------------------- latent attention
+LATENT_MAX_RANK, LATENT_MAX_ROW, LATENT_MAX_DIM = 512, 1024, 256
+
+
+def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float,
+                   inv_freq: torch.Tensor, rotary_dim: int, q_latent: torch.Tensor, pool: torch.Tensor | None, table: torch.Tensor,
+                   cu: torch.Tensor, len_before: torch.Tensor, sequences: int, n_tokens: int, status: torch.Tensor) -> None:
+    """From the partial sums of a down projection ``[q latent | kv latent | shared rotated key]``: both latents divided by
+    their root mean square (``eps`` inside the root) times their weights; the query latent goes to ``q_latent`` ``[tokens,
+    q_rank]``, and ``[kv latent | key part rotated by the position]`` to the token's row of ``pool`` ``[blocks, 1, 64, rank +
+    rot]`` (nothing is written without a pool)."""
+    for t, name in ((q_weight, "query latent norm"), (kv_weight, "latent norm"), (inv_freq, "inverse frequencies")):
+        _need(t, torch.float32, name)
+    p, splits, stride, cols = _projection(down)
+    if cols != q_rank + rank + rot or tuple(q_latent.shape) != (n_tokens, q_rank) or not q_latent.is_contiguous():
+        raise KernelError("latent_prepare: shapes do not fit the sizes")
+    if pool is not None and (pool.dtype != q_latent.dtype or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot)):
+        raise KernelError("latent_prepare: the pool must be [blocks, 1, 64, rank + rot] in the activations' dtype")
+    if (cols + 32) * 4 > 48 * 1024:
+        raise KernelError(f"latent_prepare: {cols} projected numbers per token are more than the kernel stages")
+    fn = _fn("latent_attention", "tt_latent_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                                       c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                       c_int, c_int, c_void_p, c_void_p])
+    code = dtype_code(q_latent.dtype)
+    _check(fn(p, splits, stride, q_rank, rank, rot, _ptr(q_weight), _ptr(kv_weight), eps, _ptr(inv_freq), rotary_dim, _ptr(q_latent), code,
+              _ptr(pool), code, _ptr(table), table.shape[1], 0 if pool is None else pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
+              n_tokens, _ptr(status), _stream()), "latent_prepare")
+
+
+def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor, pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
+                     len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, dim: int, rot: int, vdim: int, rank: int,
+                     inv_freq: torch.Tensor, rotary_dim: int, scale: float, window: int, splits: int, out: torch.Tensor,
+                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
+    """Causal softmax attention over a latent cache.  ``q``: float32 partial sums ``[slices, tokens, heads * (dim + rot)]`` of
+    the queries (per head ``dim`` unrotated numbers, then ``rot`` of which the first ``rotary_dim`` are rotated here);
+    ``w_key`` ``[heads * dim, rank]`` and ``w_value`` ``[heads * vdim, rank]`` expand a latent into a head's keys and values;
+    ``pool`` ``[blocks, 1, 64, rank + rot]`` holds per token the latent and the rotated key part all heads share.  Score of
+    query i and key j: ``(q_plain . w_key_h c_j + q_rot . k_rot_j) * scale`` for ``0 <= i - j < window`` (``window`` 0: every
+    earlier key); ``out`` ``[tokens, heads * vdim]``.  ``splits`` > 1 cuts the keys into slices whose partial results go
+    through ``part_acc`` ``[tokens * heads * splits * rank]`` and ``part_ml`` ``[tokens * heads * splits * 2]``."""
+    _need(inv_freq, torch.float32, "inverse frequencies")
+    if rank > LATENT_MAX_RANK or rank + rot > LATENT_MAX_ROW or dim > LATENT_MAX_DIM:
+        raise KernelError(f"latent attention takes latents of up to {LATENT_MAX_RANK}, rows of up to {LATENT_MAX_ROW} and "
+                          f"{LATENT_MAX_DIM} unrotated numbers per head; got {rank}, {rank + rot}, {dim}")
+    p, q_splits, q_stride, q_cols = _projection(q)
+    if (q_cols != heads * (dim + rot) or tuple(w_key.shape) != (heads * dim, rank) or tuple(w_value.shape) != (heads * vdim, rank)
+            or w_key.dtype != w_value.dtype or not w_key.is_contiguous() or not w_value.is_contiguous()
+            or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot) or pool.dtype != out.dtype
+            or tuple(out.shape) != (n_tokens, heads * vdim) or not out.is_contiguous()):
+        raise KernelError("latent_attention: shapes do not fit the sizes")
+    if splits > 1:
+        _need(part_acc, torch.float32, "slice sums")
+        _need(part_ml, torch.float32, "slice maxima")
+        if part_acc.numel() < n_tokens * heads * splits * rank or part_ml.numel() < n_tokens * heads * splits * 2:
+            raise KernelError("latent_attention: scratch memory for the key slices is too small")
+    fn = _fn("latent_attention", "tt_latent_attention", [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                                         c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                         c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                         c_void_p])
+    _check(fn(p, q_splits, q_stride, _ptr(w_key), _ptr(w_value), dtype_code(w_key.dtype), _ptr(pool), dtype_code(out.dtype), _ptr(table),
+              table.shape[1], pool.shape[0], _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, dim, rot, vdim, rank, _ptr(inv_freq),
+              rotary_dim, scale, window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()),
+           "latent_attention", 2 if splits > 1 else 1)
+
+
+# ------------------------------------------------------------------------------ routing
+ROUTE_MAX_EXPERTS = 512
+
+
+def route_topk(logits: torch.Tensor, top: int, groups: int, keep: int, gates: torch.Tensor, chosen: torch.Tensor,
+               weights: torch.Tensor) -> None:
+    """Routing of a mixture of experts from the router's logits (float32 partial sums ``[slices, tokens, experts]``): scores
+    are the softmax over all experts; experts form ``groups`` equal groups of neighbours, a group's score is its largest
+    expert score, and only experts of the ``keep`` best groups can be chosen; the ``top`` largest of those are chosen (ties:
+    the lower index) and weighted by score / (sum of the chosen scores + 1e-20).  ``chosen`` int32 and ``weights`` float32
+    ``[tokens, top]``; ``gates`` float32 ``[tokens, experts]`` holds the same densely, zero for experts not chosen."""
+    p, splits, stride, experts = _projection(logits)
+    tokens = logits.shape[1]
+    _need(gates, torch.float32, "gates")
+    _need(weights, torch.float32, "routing weights")
+    _need(chosen, torch.int32, "chosen experts")
+    if (experts > ROUTE_MAX_EXPERTS or not 1 <= top <= min(32, experts) or not 1 <= groups <= 32 or experts % groups
+            or not 1 <= keep <= groups):
+        raise KernelError(f"route_topk takes up to {ROUTE_MAX_EXPERTS} experts in up to 32 equal groups and up to 32 choices; got "
+                          f"{experts} experts, {groups} groups of which {keep} stay, top {top}")
+    if tuple(gates.shape) != (tokens, experts) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
+        raise KernelError("route_topk: outputs do not fit the sizes")
+    fn = _fn("routing", "tt_route_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p])
+    _check(fn(p, splits, stride, tokens, experts, top, groups, keep, _ptr(gates), _ptr(chosen), _ptr(weights), _stream()), "route_topk")
+
+
+def scale_expert_columns(act: torch.Tensor, width: int, gates: torch.Tensor) -> None:
+    """act[t, e * width + j] *= gates[t, e] for the ``experts * width`` leading columns of ``act`` (in place; columns behind
+    them stay as they are)."""
+    _need(gates, torch.float32, "gates")
+    tokens, experts = gates.shape
+    if act.dim() != 2 or act.shape[0] != tokens or act.shape[1] < experts * width or act.stride(1) != 1:
+        raise KernelError("scale_expert_columns: the activations do not fit the gates")
+    fn = _fn("routing", "tt_scale_expert_columns", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(act), dtype_code(act.dtype), tokens, act.stride(0), width, experts, _ptr(gates), _stream()), "scale_expert_columns")
 
 
 # -------------------------------------------------------------------------------- gemm

@@ -37,6 +37,8 @@ SOURCES: dict[str, list[str]] = {
     "attention_mma": [],
     "attention_tcgen05": [],
     "recurrent": [],
+    "latent_attention": [],
+    "routing": [],
 }
 
 

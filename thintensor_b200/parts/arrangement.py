@@ -85,3 +85,41 @@ class PreNormPair(Arrangement):
         ctx.residual = residual
         self.parts["ffn_norm"].forward(ctx, residual, mixed, normed)
         return self.parts["ffn"].forward(ctx, normed)
+
+
+@ARRANGEMENTS.register("parallel")
+class Parallel(Arrangement):
+    """One norm whose output both sublayers read: ``h = norm(x); x += mixer(shift(h)) + ffn(h)``.  ``shift`` (an input
+    shift, optional) stands between the norm and the mixer only; the feed-forward (optional) reads ``h`` as it is.  The
+    shift's per-sequence state is the arrangement's own."""
+
+    roles = {"norm": "norm", "shift": "shift", "mixer": "mixer", "ffn": "ffn"}
+    optional = ("shift", "ffn")
+
+    def mixers(self):
+        return [self.parts["mixer"]]
+
+    def state_needs(self):
+        return list(self.parts["shift"].state_needs()) if "shift" in self.parts else []
+
+    def device_driven(self) -> bool:
+        return all(part.device_driven() for part in self.parts.values())
+
+    def run(self, ctx, residual, pending: Delta | None, caches, states) -> Delta:
+        hidden = residual.shape[-1]
+        normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
+        self.parts["norm"].forward(ctx, residual, pending, normed)
+        # both sublayers read `normed` and nothing reads the stream before the next norm, so either may add into it
+        ctx.residual = residual
+        mixer_in = self.parts["shift"].forward(ctx, normed, states[1]) if "shift" in self.parts else normed
+        mixed = self.parts["mixer"].forward(ctx, mixer_in, caches[0], states[0])
+        if "ffn" not in self.parts:
+            return mixed
+        fed = self.parts["ffn"].forward(ctx, normed)
+        if mixed.tensor is None:
+            return fed
+        if fed.tensor is None:
+            return mixed
+        both = ctx.scratch("block.pair", (1, ctx.n_tokens, hidden), torch.float32)
+        api.weighted_pair(mixed.tensor, 1.0, fed.tensor, 1.0, both)
+        return Delta(both)

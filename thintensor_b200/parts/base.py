@@ -18,7 +18,10 @@ Roles and what each must provide:
   ``state_needs()`` what the cache must hold for it: keys and values, and any number of
   per-sequence state tensors of fixed size, each with a shape and dtype of its own.
 * ``FeedForward``: ``forward(ctx, x) -> Delta``.
-* ``Embedding``: ``forward(ctx, tokens, residual)``; ``Head``: ``forward(ctx, x) -> logits``.
+* ``Embedding``: ``forward(ctx, tokens, residual, states)``; it may declare per-sequence states like a mixer
+  (the previous token, say).  ``Head``: ``forward(ctx, x) -> logits``.
+* ``InputShift``: ``forward(ctx, x, states) -> tensor``: what a mixer reads instead of the normed rows themselves
+  (a blend with the previous token's rows, kept as a per-sequence state).
 * ``Arrangement``: wires norms, mixer and feed-forward around the residual stream.
 """
 from __future__ import annotations
@@ -48,7 +51,8 @@ class WeightDecl:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values a mixer wants kept for each sequence: ``kv_heads`` heads of
-    ``head_dim`` numbers per token (values: ``value_dim``, if given); ``window`` = only the last so many tokens."""
+    ``head_dim`` numbers per token (values: ``value_dim``, if given; 0: no value pool at all, for a mixer whose
+    values are read out of the key rows, like a shared latent); ``window`` = only the last so many tokens."""
 
     kv_heads: int
     head_dim: int
@@ -163,7 +167,21 @@ class FeedForward(Part):
 
 
 class Embedding(Part):
-    def forward(self, ctx, tokens: torch.Tensor, residual: torch.Tensor) -> None:
+    def state_needs(self) -> list[StateNeed]:
+        """Per-sequence state tensors of fixed size, zero when a sequence starts (see :meth:`Mixer.state_needs`)."""
+        return []
+
+    def forward(self, ctx, tokens: torch.Tensor, residual: torch.Tensor, states: list[torch.Tensor] | None = None) -> None:
+        raise NotImplementedError
+
+
+class InputShift(Part):
+    """Replaces a mixer's input rows by a function of them and of the rows of the tokens before."""
+
+    def state_needs(self) -> list[StateNeed]:
+        return []
+
+    def forward(self, ctx, x: torch.Tensor, states: list[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -187,8 +205,14 @@ class Arrangement:
         two); each gets a cache and states of its own."""
         return []
 
+    def state_needs(self) -> list[StateNeed]:
+        """Per-sequence states of the arrangement itself (of a part of its that is no mixer); ``run`` finds them
+        behind the mixers': ``states[len(mixers())]``."""
+        return []
+
     def run(self, ctx, residual: torch.Tensor, pending: Delta | None, caches: list, states: list[list[torch.Tensor]]) -> Delta | None:
-        """``caches[i]`` and ``states[i]`` belong to ``mixers()[i]``."""
+        """``caches[i]`` and ``states[i]`` belong to ``mixers()[i]``; an arrangement with states of its own gets one
+        more entry of each behind them."""
         raise NotImplementedError
 
     def device_driven(self) -> bool:
@@ -229,6 +253,7 @@ POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 EMBEDDINGS = Registry("embedding")
+SHIFTS = Registry("input shift")
 HEADS = Registry("head")
 ARRANGEMENTS = Registry("arrangement")
 
@@ -238,6 +263,7 @@ REGISTRIES = {
     "mixer": MIXERS,
     "ffn": FEED_FORWARDS,
     "embedding": EMBEDDINGS,
+    "shift": SHIFTS,
     "head": HEADS,
     "arrangement": ARRANGEMENTS,
 }

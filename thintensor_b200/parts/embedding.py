@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api
-from .base import EMBEDDINGS, HEADS, Embedding, Head, WeightDecl
+from .base import EMBEDDINGS, HEADS, Embedding, Head, StateNeed, WeightDecl
 from .linear import Linear
 
 
@@ -30,8 +30,41 @@ class TokenEmbedding(Embedding):
     def device_driven(self) -> bool:
         return True
 
-    def forward(self, ctx, tokens, residual) -> None:
+    def forward(self, ctx, tokens, residual, states=None) -> None:
         api.embed_gather(self.table, tokens, residual, self.scale, ctx.status)
+
+
+@EMBEDDINGS.register("table_pair_hash")
+class PairHashEmbedding(TokenEmbedding):
+    """The token's row plus a row of a second table chosen by the pair (previous token, token):
+    ``h0 = E[token] * scale + P[(previous * mul_prev + token * mul_cur) mod buckets]``, and ``P[buckets]`` (the last row)
+    for a sequence's first token.  The previous token is a per-sequence state (int32, the token plus one; zero: none yet),
+    so prompts cut into steps and decoding continue where the sequence stands."""
+
+    def __init__(self, vocab: int, hidden: int, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0, name: str = "weight",
+                 pair_name: str = "pair.weight"):
+        super().__init__(vocab, hidden, scale, name)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("the pair table needs at least one bucket and multipliers that are not negative")
+        self.pair_name = pair_name
+        self.pair_table: torch.Tensor | None = None
+
+    def weights(self) -> dict[str, WeightDecl]:
+        return {**super().weights(), self.pair_name: WeightDecl((self.buckets + 1, self.hidden))}
+
+    def state_needs(self) -> list[StateNeed]:
+        return [StateNeed((), torch.int32)]
+
+    def bind(self, tensors, dtype, device) -> None:
+        super().bind(tensors, dtype, device)
+        self.pair_table = tensors[self.pair_name].to(self.table.dtype).contiguous()
+
+    def forward(self, ctx, tokens, residual, states=None) -> None:
+        if not states:
+            raise RuntimeError("the pair embedding needs its per-sequence state (the previous token)")
+        api.embed_pair_gather(self.table, self.pair_table, tokens, ctx.cu, ctx.slots, ctx.sequences, states[0], residual, self.buckets,
+                              self.mul_prev, self.mul_cur, self.scale, ctx.status)
 
 
 @HEADS.register("linear")

@@ -1,0 +1,117 @@
+"""Causal softmax attention whose keys and values are expansions of one cached latent per token.
+
+Queries take a low-rank path: ``c_q = rmsnorm(W_dq x)`` (weight and eps), ``q = W_uq c_q``, per head ``dim``
+unrotated numbers followed by ``rot_dim`` numbers that are rotated by the position.  Keys and values share a
+latent: ``W_dkv x`` has ``kv_rank + rot_dim`` rows; the first ``kv_rank``, RMS-normed, are the latent ``c``, the
+rest are one rotated key part that all heads share.  Per head ``k = [W_uk c | k_rot]`` and ``v = W_uv c``; the
+score is ``(q . k) * scale`` over the last ``window`` positions (or all of them), softmax, then ``W_o`` on the
+concatenated heads.
+
+Only ``[c | k_rot]`` is cached: one row per token, one key/value head, no value pool.  Neither keys nor values
+are ever formed: the kernel folds ``W_uk`` into the query (``a = W_uk_h^T q_h``, so that ``q_h . W_uk_h c = a . c``)
+and applies ``W_uv_h`` once to the softmax-weighted sum of latents.  Norms, positions, angles, scores and softmax
+weights are float32 in both dtypes.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import api
+from .attention import kv_splits
+from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, RotaryTable, WeightDecl
+from .linear import Linear
+from .spec import PartSpec
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    NAMES = {"dq": "q_a_proj.weight", "dq_norm": "q_a_norm.weight", "uq": "q_b_proj.weight", "dkv": "kv_a_proj.weight",
+             "dkv_norm": "kv_a_norm.weight", "uk": "k_b_proj.weight", "uv": "v_b_proj.weight", "o": "o_proj.weight"}
+
+    def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int, scale: float,
+                 eps: float, position: PartSpec | None = None, window: int | None = None, names: dict | None = None):
+        self.hidden, self.heads, self.dim, self.rot_dim = int(hidden), int(heads), int(dim), int(rot_dim)
+        self.value_dim, self.q_rank, self.kv_rank = int(value_dim), int(q_rank), int(kv_rank)
+        self.scale, self.eps = float(scale), float(eps)
+        self.window = None if not window else int(window)
+        if self.kv_rank > api.LATENT_MAX_RANK or self.kv_rank + self.rot_dim > api.LATENT_MAX_ROW or self.dim > api.LATENT_MAX_DIM:
+            raise ValueError(f"latent attention takes latents of up to {api.LATENT_MAX_RANK} numbers, cache rows of up to "
+                             f"{api.LATENT_MAX_ROW} and {api.LATENT_MAX_DIM} unrotated numbers per head")
+        self.names = {**self.NAMES, **(names or {})}
+        position = position or PartSpec("none", {"head_dim": max(self.rot_dim, 1)})
+        self.position = POSITION_ENCODINGS.build(position.kind, dict(position.params))
+        if self.position.kind not in ("rotary", "none"):
+            raise ValueError(f"latent attention applies rotary position encodings or none, not one of kind {self.position.kind!r}")
+        self.rot: RotaryTable | None = None
+        self.down: Linear | None = None
+        self.up_q: Linear | None = None
+        self.out: Linear | None = None
+
+    def weights(self) -> dict[str, WeightDecl]:
+        n = self.names
+        return {
+            n["dq"]: WeightDecl((self.q_rank, self.hidden)),
+            n["dq_norm"]: WeightDecl((self.q_rank,), init="norm"),
+            n["uq"]: WeightDecl((self.heads * (self.dim + self.rot_dim), self.q_rank)),
+            n["dkv"]: WeightDecl((self.kv_rank + self.rot_dim, self.hidden)),
+            n["dkv_norm"]: WeightDecl((self.kv_rank,), init="norm"),
+            n["uk"]: WeightDecl((self.heads * self.dim, self.kv_rank)),
+            n["uv"]: WeightDecl((self.heads * self.value_dim, self.kv_rank)),
+            n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim)),
+        }
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(1, self.kv_rank + self.rot_dim, self.window, 0)       # one row per token, values read from the key rows
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.position.bind({}, dtype, device)
+        if self.position.kind == "rotary":
+            self.rot = self.position.rotary()
+            if self.rot.interleaved or self.rot.attention_scaling != 1.0:
+                raise ValueError("latent attention rotates halves of the rotated part and does not scale the rotation")
+            if self.rot.rotary_dim % 2 or self.rot.rotary_dim > self.rot_dim:
+                raise ValueError(f"the rotation takes an even number of at most {self.rot_dim} numbers, got {self.rot.rotary_dim}")
+        else:
+            self.rot = RotaryTable(torch.zeros(1, dtype=torch.float32, device=device), 0, 1.0)
+        n = self.names
+        self.down = Linear(torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0))     # [q latent | kv latent | shared key part]
+        self.up_q = Linear(tensors[n["uq"]])
+        self.out = Linear(tensors[n["o"]])
+        self.q_norm = tensors[n["dq_norm"]].to(torch.float32).contiguous()
+        self.kv_norm = tensors[n["dkv_norm"]].to(torch.float32).contiguous()
+        self.w_key, self.w_value = tensors[n["uk"]].contiguous(), tensors[n["uv"]].contiguous()
+
+    def projections(self) -> list:
+        return [self.down, self.up_q, Linear(self.w_key), Linear(self.w_value), self.out]
+
+    def vectors(self) -> list[torch.Tensor]:
+        return [self.q_norm, self.kv_norm]
+
+    def device_driven(self) -> bool:
+        return True
+
+    def forward(self, ctx, x, cache, states) -> Delta:
+        if cache is None or cache.k_pool is None:
+            raise RuntimeError("latent attention needs a cache with storage")
+        table = ctx.tables[cache.group]
+        rot = self.rot
+        down = self.down(ctx, x, "latent.down")
+        q_latent = ctx.scratch("latent.q_latent", (ctx.n_tokens, self.q_rank))
+        api.latent_prepare(down, self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm, self.eps, rot.inv_freq,
+                           rot.rotary_dim, q_latent, cache.k_pool if cache.writes else None, table, ctx.cu, ctx.len_before,
+                           ctx.sequences, ctx.n_tokens, ctx.status)
+        q = self.up_q(ctx, q_latent, "latent.up_q")
+        mixed = ctx.scratch("latent.mixed", (ctx.n_tokens, self.heads * self.value_dim))
+        splits = 1
+        if ctx.decode:
+            # keys of a decode step are cut into slices until the (token, head) warps fill the GPU; a window bounds the keys
+            reach = ctx.max_total if self.window is None else min(self.window, ctx.max_total)
+            splits = min(kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(ctx.status.device)), max(1, reach // 256))
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = ctx.scratch("latent.part_acc", (ctx.n_tokens * self.heads * splits * self.kv_rank,), torch.float32)
+            part_ml = ctx.scratch("latent.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
+        api.latent_attention(q, self.w_key, self.w_value, cache.k_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
+                             self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, rot.inv_freq, rot.rotary_dim, self.scale,
+                             self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+        return self.out.delta(ctx, mixed, "latent.out")

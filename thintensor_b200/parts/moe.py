@@ -1,0 +1,91 @@
+"""Mixture of experts with group-limited top-k routing and an optional shared expert.
+
+Every expert is a gated feed-forward ``down(f(gate x) * up x)`` without biases.  The router's logits ``W_r x`` are
+float32; scores are their softmax over all experts.  Experts form ``groups`` equal groups of neighbours, a group's
+score is the largest score in it, and only experts of the ``keep`` best groups can be chosen; each token takes the
+``top`` largest of those, weighted by score / (sum of the chosen scores + 1e-20).  A shared expert of its own width
+runs for every token and is added unweighted.
+
+The experts run as ONE gated product over the concatenation of all experts' gate and up rows (the shared expert's
+behind them) and ONE down product over the concatenated columns: a token's activations are multiplied by its
+routing weight per expert (zero for experts it did not choose) in between, so the down product's sum over its input
+IS the weighted sum over experts.  Every matrix is read once per step whatever the routing, which is what a decode
+step of more than a few sequences does anyway, and prompts keep the tensor-core tiles full; the price is the
+arithmetic of the experts a token did not choose.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import api
+from .base import FEED_FORWARDS, Delta, FeedForward, WeightDecl
+from .linear import GatedLinear, Linear
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts(FeedForward):
+    NAMES = {"router": "router.weight", "expert": "experts.{}.", "shared": "shared.", "gate": "gate_proj.weight", "up": "up_proj.weight",
+             "down": "down_proj.weight"}
+
+    def __init__(self, hidden: int, experts: int, top: int, inter: int, groups: int = 1, keep: int = 1, shared_inter: int = 0,
+                 activation: str = "silu", names: dict | None = None):
+        self.hidden, self.experts, self.top, self.inter = int(hidden), int(experts), int(top), int(inter)
+        self.groups, self.keep, self.shared_inter = int(groups), int(keep), int(shared_inter or 0)
+        if activation not in api.GATE_ACTIVATIONS:
+            raise ValueError(f"gate activation {activation!r} is not one of {sorted(api.GATE_ACTIVATIONS)}")
+        if self.experts % self.groups or not 1 <= self.keep <= self.groups:
+            raise ValueError(f"{experts} experts do not form {groups} equal groups of which {keep} stay")
+        if not 1 <= self.top <= self.keep * (self.experts // self.groups):
+            raise ValueError(f"a token cannot choose {top} experts out of {self.keep * (self.experts // self.groups)} allowed ones")
+        if self.experts > api.ROUTE_MAX_EXPERTS or self.groups > 32 or self.top > 32:
+            raise ValueError(f"the routing kernel takes up to {api.ROUTE_MAX_EXPERTS} experts, 32 groups and 32 choices")
+        self.activation = activation
+        self.names = {**self.NAMES, **(names or {})}
+        self.router: Linear | None = None
+        self.gate_up: GatedLinear | None = None
+        self.down: Linear | None = None
+
+    def _expert_names(self, prefix: str) -> tuple[str, str, str]:
+        n = self.names
+        return prefix + n["gate"], prefix + n["up"], prefix + n["down"]
+
+    def _prefixes(self) -> list[tuple[str, int]]:
+        out = [(self.names["expert"].format(e), self.inter) for e in range(self.experts)]
+        if self.shared_inter:
+            out.append((self.names["shared"], self.shared_inter))
+        return out
+
+    def weights(self) -> dict[str, WeightDecl]:
+        out = {}
+        for prefix, inter in self._prefixes():
+            gate, up, down = self._expert_names(prefix)
+            out[gate] = WeightDecl((inter, self.hidden))
+            out[up] = WeightDecl((inter, self.hidden))
+            out[down] = WeightDecl((self.hidden, inter))
+        out[self.names["router"]] = WeightDecl((self.experts, self.hidden))
+        return out
+
+    def bind(self, tensors, dtype, device) -> None:
+        names = [self._expert_names(prefix) for prefix, _ in self._prefixes()]
+        self.gate_up = GatedLinear(torch.cat([tensors[g] for g, _, _ in names], dim=0), torch.cat([tensors[u] for _, u, _ in names], dim=0),
+                                   None, None, self.activation)
+        self.down = Linear(torch.cat([tensors[d] for _, _, d in names], dim=1))
+        # the router runs the exact float32 product in both dtypes
+        self.router = Linear(tensors[self.names["router"]].to(torch.float32))
+
+    def projections(self) -> list:
+        return [self.router, self.gate_up.fused, self.down]
+
+    def device_driven(self) -> bool:
+        return True
+
+    def forward(self, ctx, x) -> Delta:
+        tokens = ctx.n_tokens
+        logits = self.router(ctx, x, "moe.router")
+        gates = ctx.scratch("moe.gates", (tokens, self.experts), torch.float32)
+        chosen = ctx.scratch("moe.chosen", (tokens, self.top), torch.int32)
+        weights = ctx.scratch("moe.weights", (tokens, self.top), torch.float32)
+        api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights)
+        act = self.gate_up(ctx, x, "moe.gate_up")
+        api.scale_expert_columns(act, self.inter, gates)
+        return self.down.delta(ctx, act, "moe.down")

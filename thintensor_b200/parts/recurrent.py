@@ -24,6 +24,14 @@ value_dim, ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T
 divided by its root mean square, multiplied by a weight of ``value_dim`` numbers that the heads
 share, and by ``silu(W_g h)``.
 
+``decay_linear_attention``: linear attention with a fixed decay per head and neither softmax nor
+denominator: per head, with S of shape key_dim x value_dim, ``S <- decay_h S + k v^T`` and ``o = S^T q``.
+Two published forms are parameter sets of it.  Lightning attention: ``activation="silu"`` on q, k and v,
+the read-out of all heads RMS-normed together with a weight (``norm="all"``) and gated by
+``sigmoid(W_g h)``.  Retention: q and k rotated by the position (``position``), k times
+``key_dim ** -0.5`` (``key_scale``), every head's read-out divided by its own root mean square without a
+weight (``norm="head"``) and gated by ``silu(W_g h)``.  There is no convolution; the only state is S.
+
 Decays, step sizes, gates of the recurrence, unit norms and the states are float32 whatever the
 model's dtype; only the normed read-out that feeds the output projection is narrowed.
 """
@@ -32,8 +40,9 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api
-from .base import MIXERS, Delta, Mixer, StateNeed, WeightDecl
+from .base import MIXERS, POSITION_ENCODINGS, Delta, Mixer, RotaryTable, StateNeed, WeightDecl
 from .linear import Linear
+from .spec import PartSpec
 
 
 def _f32(t: torch.Tensor) -> torch.Tensor:
@@ -182,3 +191,92 @@ class GatedDelta(Mixer):
         gated = ctx.scratch("delta.gated", (tokens, self.v))
         api.gated_group_norm(read, self.value_dim, proj, gate_col, self.norm, self.eps, False, gated)
         return self.out.delta(ctx, gated, "delta.out")
+
+
+@MIXERS.register("decay_linear_attention")
+class DecayLinearAttention(Mixer):
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight", "norm": "norm.weight",
+             "out": "o_proj.weight"}
+
+    def __init__(self, hidden: int, heads: int, key_dim: int, value_dim: int, decay, activation: str | None = None,
+                 position: PartSpec | None = None, key_scale: float = 1.0, norm: str = "head", norm_weight: bool = False,
+                 gate: str = "silu", eps: float = 1e-6, names: dict | None = None):
+        self.hidden, self.heads, self.key_dim, self.value_dim = int(hidden), int(heads), int(key_dim), int(value_dim)
+        self.decay = tuple(float(d) for d in decay)
+        if len(self.decay) != self.heads:
+            raise ValueError(f"{len(self.decay)} decays for {self.heads} heads")
+        if activation not in (None, "silu"):
+            raise ValueError(f"q, k and v pass silu or nothing, not {activation!r}")
+        if norm not in ("head", "all"):
+            raise ValueError(f"the read-out is normed per head or over all heads, not {norm!r}")
+        if gate not in api.NORM_GATES:
+            raise ValueError(f"the gate is one of {sorted(api.NORM_GATES)}, not {gate!r}")
+        if not 1 <= self.key_dim <= 256:
+            raise ValueError("the recurrent kernels take key sizes of up to 256")
+        self.activation, self.key_scale, self.norm, self.norm_weight = activation, float(key_scale), norm, bool(norm_weight)
+        self.gate, self.eps = gate, float(eps)
+        self.qk, self.v = self.heads * self.key_dim, self.heads * self.value_dim
+        self.names = {**self.NAMES, **(names or {})}
+        position = position or PartSpec("none", {"head_dim": self.key_dim})
+        self.position = POSITION_ENCODINGS.build(position.kind, dict(position.params))
+        if self.position.kind not in ("rotary", "none"):
+            raise ValueError(f"linear attention applies rotary position encodings or none, not one of kind {self.position.kind!r}")
+        self.rot: RotaryTable | None = None
+        self.proj: Linear | None = None
+        self.out: Linear | None = None
+
+    def weights(self) -> dict[str, WeightDecl]:
+        n = self.names
+        out = {
+            n["q"]: WeightDecl((self.qk, self.hidden)),
+            n["k"]: WeightDecl((self.qk, self.hidden)),
+            n["v"]: WeightDecl((self.v, self.hidden)),
+            n["g"]: WeightDecl((self.v, self.hidden)),
+            n["out"]: WeightDecl((self.hidden, self.v)),
+        }
+        if self.norm_weight:
+            out[n["norm"]] = WeightDecl((self.v if self.norm == "all" else self.value_dim,), init="norm")
+        return out
+
+    def state_needs(self) -> list[StateNeed]:
+        return [StateNeed((self.heads, self.value_dim, self.key_dim), torch.float32)]
+
+    def bind(self, tensors, dtype, device) -> None:
+        n = self.names
+        self.position.bind({}, dtype, device)
+        self.rot = None
+        if self.position.kind == "rotary":
+            self.rot = self.position.rotary()
+            if self.rot.interleaved or self.rot.attention_scaling != 1.0 or self.rot.rotary_dim % 2 or self.rot.rotary_dim > self.key_dim:
+                raise ValueError("linear attention rotates halves of an even part of the head and does not scale the rotation")
+        # one product for everything linear in the input: [q | k | v | gate]
+        self.proj = Linear(torch.cat([tensors[n[key]] for key in ("q", "k", "v", "g")], dim=0))
+        self.out = Linear(tensors[n["out"]])
+        self.decays = torch.tensor(self.decay, dtype=torch.float32, device=device)
+        count = self.v if self.norm == "all" else self.value_dim
+        self.norm_w = _f32(tensors[n["norm"]]) if self.norm_weight else torch.ones(count, dtype=torch.float32, device=device)
+
+    def projections(self) -> list:
+        return [self.proj, self.out]
+
+    def vectors(self) -> list[torch.Tensor]:
+        return [self.norm_w] if self.norm_weight else []
+
+    def device_driven(self) -> bool:
+        return True
+
+    def forward(self, ctx, x, cache, states) -> Delta:
+        (recurrent,) = states
+        tokens = ctx.n_tokens
+        proj = self.proj(ctx, x, "linear_attention.in")
+        vkq = ctx.scratch("linear_attention.vkq", (tokens, self.v + 2 * self.qk), torch.float32)
+        rotary_dim = self.rot.rotary_dim if self.rot is not None else 0
+        api.linear_attention_prepare(proj, self.heads, self.key_dim, self.value_dim, self.activation == "silu",
+                                     self.rot.inv_freq if rotary_dim else None, rotary_dim, self.key_scale, vkq, ctx.cu, ctx.len_before,
+                                     ctx.sequences, tokens)
+        read = ctx.scratch("linear_attention.read", (tokens, self.v), torch.float32)
+        api.decay_scan(vkq, self.decays, recurrent, read, ctx.cu, ctx.slots, ctx.sequences, self.heads, self.key_dim, self.value_dim)
+        gated = ctx.scratch("linear_attention.gated", (tokens, self.v))
+        api.gated_group_norm(read, self.v if self.norm == "all" else self.value_dim, proj, 2 * self.qk + self.v, self.norm_w, self.eps,
+                             False, gated, self.gate)
+        return self.out.delta(ctx, gated, "linear_attention.out")
