@@ -24,6 +24,16 @@ from pathlib import Path
 import numpy as np
 import torch
 
+# What stands in for the narrowing of activations: None (exact), or a function applied wherever an engine that
+# multiplies bfloat16 matrices narrows its operand (the input of every projection, cached latents, the read-outs before
+# the output projections).  ``forward(..., narrow=f)`` sets it.
+_narrow = None
+
+
+def nar(x):
+    return x if _narrow is None else _narrow(x)
+
+
 _NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64}
 
 
@@ -107,12 +117,14 @@ def latent_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, D, R, V, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = torch.arange(T)
-    cq = rms_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
+    h = nar(h)
+    cq = nar(rms_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps))
     q = (cq @ w[p + "uq"].T).reshape(T, H, D + R)
-    q_plain, q_rot = q[..., :D], rotate_halves(q[..., D:], pos, m["rot"]["dims"], m["rot"]["base"])
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    q_plain, q_rot = q[..., :D], rotate_halves(q[..., D:], pos, rot["dims"], rot["base"])
     down = h @ w[p + "dkv"].T
-    c = rms_norm(down[:, :rank], w[p + "dkv.norm"], eps)
-    k_rot = rotate_halves(down[:, rank:], pos, m["rot"]["dims"], m["rot"]["base"])      # one for all heads
+    c = nar(rms_norm(down[:, :rank], w[p + "dkv.norm"], eps))
+    k_rot = nar(rotate_halves(down[:, rank:], pos, rot["dims"], rot["base"]))      # one for all heads
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, D)
     v = (c @ w[p + "uv"].T).reshape(T, H, V)
     window = (m.get("mask") or {}).get("size")
@@ -122,7 +134,7 @@ def latent_attention(h, w, p, m, eps):
         s = (torch.einsum("hd,jhd->hj", q_plain[t], k_plain[lo:t + 1]) + q_rot[t] @ k_rot[lo:t + 1].T) * m["scale"]
         a = torch.softmax(s, dim=-1)
         out[t] = torch.einsum("hj,jhv->hv", a, v[lo:t + 1])
-    return out.reshape(T, H * V) @ w[p + "o"].T
+    return nar(out.reshape(T, H * V)) @ w[p + "o"].T
 
 
 def decayed_outer_product_scan(q, k, v, decay):
@@ -139,17 +151,19 @@ def decayed_outer_product_scan(q, k, v, decay):
 
 def lightning(h, w, p, m, eps):
     T = h.shape[0]
+    h = nar(h)
     H, D, V = m["heads"], m["dim"], m["vdim"]
     q = silu(h @ w[p + "q"].T).reshape(T, H, D)
     k = silu(h @ w[p + "k"].T).reshape(T, H, D)
     v = silu(h @ w[p + "v"].T).reshape(T, H, V)
     o = decayed_outer_product_scan(q, k, v, m["decay"]).reshape(T, H * V)
     o = rms_norm(o, w[p + "norm"], eps) * sigmoid(h @ w[p + "g"].T)
-    return o @ w[p + "o"].T
+    return nar(o) @ w[p + "o"].T
 
 
 def retention(h, w, p, m, eps):
     T = h.shape[0]
+    h = nar(h)
     H, D, V = m["heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
     q = (h @ w[p + "q"].T).reshape(T, H, D)
@@ -160,7 +174,7 @@ def retention(h, w, p, m, eps):
     k = k * D ** -0.5
     v = (h @ w[p + "v"].T).reshape(T, H, V)
     o = rms_norm(decayed_outer_product_scan(q, k, v, m["decay"]), None, eps).reshape(T, H * V)
-    return (o * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return nar(o * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
 MIXERS = {"latent_attention": latent_attention, "lightning": lightning, "retention": retention}
@@ -168,7 +182,7 @@ MIXERS = {"latent_attention": latent_attention, "lightning": lightning, "retenti
 
 # ------------------------------------------------------------------------- feed-forward
 def gated_expert(h, w, p):
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    return nar(silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def route(scores, top, groups, keep):
@@ -186,6 +200,7 @@ def route(scores, top, groups, keep):
 
 def mixture(h, w, p, mlp):
     r = mlp["router"]
+    h = nar(h)
     groups = r.get("groups") or {"count": 1, "keep": 1}
     scores = torch.softmax(h @ w[p + "router"].T, dim=-1)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
@@ -199,19 +214,28 @@ def mixture(h, w, p, mlp):
 
 
 # -------------------------------------------------------------------------------- model
-def forward(config, w, tokens, dtype=torch.float64, layers_out=None):
+def forward(config, w, tokens, dtype=torch.float64, layers_out=None, narrow=None):
     """Logits [tokens, vocab] of one whole sequence.  ``layers_out``: a list that receives the stream after each layer."""
+    global _narrow
+    _narrow = narrow
+    try:
+        return _forward(config, w, tokens, dtype, layers_out)
+    finally:
+        _narrow = None
+
+
+def _forward(config, w, tokens, dtype, layers_out):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = config["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.int64)
     x = embed(tokens, w["embed"], w.get("bigram"), (config.get("embedding") or {}).get("bigram"))
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = rms_norm(x, w[p + "norm1"], eps)
+        h = nar(rms_norm(x, w[p + "norm1"], eps))
         add = MIXERS[layer["type"]](token_shift(h, w[p + "shift"]), w, p + "mix.", layer["mixer"], eps)
         if layer.get("mlp") is not None:
             add = add + mixture(h, w, p + "mlp.", layer["mlp"])
         x = x + add
         if layers_out is not None:
             layers_out.append(x.clone())
-    return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    return nar(rms_norm(x, w["final.norm"], eps)) @ w["head"].T

@@ -103,6 +103,7 @@ class MoeSizes:
     groups: int = 1
     keep: int = 1
     shared_ff: int = 0      # 0: no shared expert
+    grouped: bool = True    # whether config.json spells the groups out (one group of which one stays says the same)
 
     @staticmethod
     def from_dict(raw: dict, where: str) -> "MoeSizes":
@@ -114,7 +115,7 @@ class MoeSizes:
         sizes = MoeSizes(_int(router, "experts", where + ".router"), _int(router, "top", where + ".router"), _int(expert, "ff", where + ".expert"),
                          _int(groups, "count", where + ".router.groups") if groups else 1,
                          _int(groups, "keep", where + ".router.groups") if groups else 1,
-                         _int(shared, "ff", where + ".shared") if shared else 0)
+                         _int(shared, "ff", where + ".shared") if shared else 0, bool(groups))
         if sizes.experts % sizes.groups or sizes.keep > sizes.groups:
             raise ConfigError(f"config.json: {where}: {sizes.experts} experts do not form {sizes.groups} equal groups of which {sizes.keep} stay")
         if sizes.top > sizes.keep * (sizes.experts // sizes.groups):
@@ -122,8 +123,11 @@ class MoeSizes:
         return sizes
 
     def to_dict(self) -> dict:
-        out: dict[str, Any] = {"expert": {"ff": self.ff}, "kind": "moe",
-                               "router": {"experts": self.experts, "groups": {"count": self.groups, "keep": self.keep}, "top": self.top}}
+        router: dict[str, Any] = {"experts": self.experts}
+        if self.grouped:
+            router["groups"] = {"count": self.groups, "keep": self.keep}
+        router["top"] = self.top
+        out: dict[str, Any] = {"expert": {"ff": self.ff}, "kind": "moe", "router": router}
         if self.shared_ff:
             out["shared"] = {"ff": self.shared_ff}
         return out
