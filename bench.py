@@ -109,6 +109,16 @@ def reference_arm(config: dict, steps: int, warmup: int) -> int:
 
 
 FAMALORN_SHAPES = {"1b": "famalorn-w2048", "3b": "famalorn-w3072"}
+NERUZEN_SHAPES = {"1b": "neruzen-w2048", "3b": "neruzen-w3072"}
+
+
+def neruzen_pair(size: str) -> tuple[dict, dict]:
+    """(Neruzen config.json, Famalorn config.json) of one size from the table of named shapes: the same width, vocabulary
+    and number of layers (six).  Famalorn, the decoder with recurrent mixers that the library already had, is the closest
+    model: its Mamba-2 scan is the kernel Neruzen's linear attentions run, its attention branch the like of the latent
+    attention.  Every Neruzen layer has the mixture of experts: 16 experts of 1,024 of which a token takes 4, and a shared
+    expert of 4,096, so a token's feed-forward is as wide as Famalorn's dense one (8,192)."""
+    return json.loads(json.dumps(SHAPES[NERUZEN_SHAPES[size]])), json.loads(json.dumps(SHAPES[FAMALORN_SHAPES[size]]))
 
 
 def famalorn_pair(size: str) -> tuple[dict, dict]:
@@ -123,17 +133,19 @@ def famalorn_pair(size: str) -> tuple[dict, dict]:
 
 def design_bench(args) -> int:
     """``--design famalorn``: prefill and decode of the Famalorn design beside the Llama decoder at equal size (random
-    weights, bfloat16), with each step's time by class of kernel against that class's bound.  One JSON line."""
+    weights, bfloat16), with each step's time by class of kernel against that class's bound.  ``--design neruzen``: the
+    same for the Neruzen design beside Famalorn.  One JSON line."""
     import thintensor_b200
     from thintensor_b200.benchmark import class_fractions, measure_classes, measure_decode, measure_prefill
 
     pk = peaks()
     import torch
-    out = {"bench": "Famalorn beside Llama at equal width, feed-forward, vocabulary and layers; random weights, bfloat16",
+    names, pair = (("famalorn", "llama"), famalorn_pair) if args.design == "famalorn" else (("neruzen", "famalorn"), neruzen_pair)
+    out = {"bench": f"{names[0].capitalize()} beside {names[1].capitalize()} at equal width, feed-forward, vocabulary and layers; random weights, bfloat16",
            "prompt_len": args.prompt_len, "batch": args.batch, "peaks": pk, "sizes": {}}
     for size in args.sizes.split(","):
         entry = out["sizes"][size] = {}
-        for name, raw in zip(("famalorn", "llama"), famalorn_pair(size)):
+        for name, raw in zip(names, pair(size)):
             runtime = thintensor_b200.random_model(raw, seed=0, dtype="bf16", device="cuda:0")
             vocab = raw.get("vocab") or raw["vocab_size"]
             g = torch.Generator().manual_seed(1)
@@ -177,7 +189,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     parser.add_argument("--shape", choices=sorted(SHAPE_NAMES), default="1b", help="with --only: layer sizes of another model of the family")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
-    parser.add_argument("--design", choices=["famalorn"], help="measure this design beside the Llama decoder at equal size instead of the headline")
+    parser.add_argument("--design", choices=["famalorn", "neruzen"],
+                        help="measure this design beside the closest model the library has at equal size (Famalorn beside Llama, Neruzen beside Famalorn) instead of the headline")
     parser.add_argument("--sizes", default="1b,3b", help="with --design: which sizes (1b: width 2,048; 3b: width 3,072)")
     args = parser.parse_args()
     if args.design:

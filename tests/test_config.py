@@ -111,8 +111,8 @@ def test_named_shapes_are_whole_configurations():
     assert tuple(shapes) == SHAPE_NAMES
     for name, raw in shapes.items():
         arch, config = load_config(raw)
-        if name.startswith("famalorn"):
-            assert arch.name == "Famalorn" and config.width == raw["width"] and config.to_dict() == raw, name
+        if name.startswith(("famalorn", "neruzen")):
+            assert arch.name == name.split("-")[0].capitalize() and config.width == raw["width"] and config.to_dict() == raw, name
         else:
             assert arch.name == "LlamaForCausalLM" and config.hidden_size == raw["hidden_size"], name
     one_b = load_config(shapes["llama-3.2-1b"])[1]

@@ -19,7 +19,7 @@ from .sampling.sampler import SamplingParams
 
 # Named shapes for benchmarks with random weights, each a whole config.json: the three Llama 3
 # models the reference's reports measure, two tiny ones that differ in every size and option, and
-# two Famalorn models of six layers at the widths of the 1B and 3B Llama shapes.
+# two Famalorn and two Neruzen models of six layers at the widths of the 1B and 3B Llama shapes.
 # They are data (config/shapes.json), read here and by bench.py.
 SHAPES: dict[str, dict] = json.loads((Path(__file__).resolve().parent / "config" / "shapes.json").read_text(encoding="utf-8"))
 
@@ -82,6 +82,15 @@ def kv_read_bytes_per_token(model) -> int:
     return sum(need.kv_heads * (need.head_dim + need.v_dim) * width for need in kv if need is not None)
 
 
+def kv_read_bytes(model, context: float) -> float:
+    """Bytes of keys and values a decode step reads for one sequence of ``context`` cached tokens: a run with a window
+    reads only the window's tokens."""
+    kv, _, _ = model.cache_needs()
+    width = torch.empty((), dtype=model.dtype).element_size()
+    return sum(need.kv_heads * (need.head_dim + need.v_dim) * width * (context if need.window is None else min(context, need.window))
+               for need in kv if need is not None)
+
+
 def state_bytes_per_sequence(model) -> int:
     """Bytes of fixed-size state (recurrent matrices, carried convolution inputs) one sequence holds over all layers;
     a decode step reads and writes each of them once."""
@@ -107,13 +116,20 @@ def linear_flops_per_token(model) -> int:
 
 
 def attention_flops(model, tokens: int) -> float:
-    """Causal attention of one sequence of ``tokens`` tokens: QK^T and PV over t(t+1)/2 pairs."""
+    """Causal attention of one sequence of ``tokens`` tokens: QK^T and PV over t(t+1)/2 pairs (fewer under a
+    window).  A mixer whose keys and values are not what it caches says what a pair costs (``pair_dims``: numbers of a
+    score's dot product and of a value)."""
     flops = 0.0
     kv, _, _ = model.cache_needs()
     for index, run in enumerate(model.spec.schedule):
         for user, mixer in zip(model.users[index], model.layers[run.layer].mixers()):
             if kv[user] is not None:
-                flops += 2.0 * (tokens * (tokens + 1) / 2) * (kv[user].head_dim + kv[user].v_dim) * getattr(mixer, "heads", kv[user].kv_heads)
+                window = kv[user].window
+                pairs = tokens * (tokens + 1) / 2
+                if window is not None and window < tokens:
+                    pairs = window * (window + 1) / 2 + (tokens - window) * window
+                dims = sum(getattr(mixer, "pair_dims", (kv[user].head_dim, kv[user].v_dim)))
+                flops += 2.0 * pairs * dims * getattr(mixer, "heads", kv[user].kv_heads)
     return flops
 
 
@@ -172,12 +188,12 @@ def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[i
     and its attention against it too (the cache it reads); the rest (norms, rotation, embedding,
     sampling) has no bound worth naming and is given as time alone.  Times are those of kernels run
     one after another (see :func:`measure_classes`)."""
-    recurrent = ("tt_mamba2_scan", "tt_delta_scan", "tt_causal_conv", "tt_gated_group_norm")
+    recurrent = ("tt_mamba2_scan", "tt_delta_scan", "tt_causal_conv", "tt_gated_group_norm", "tt_decay_scan", "tt_linear_attention_prepare")
 
     def split(spans: dict) -> dict:
         out = {"products": 0.0, "attention": 0.0, "recurrence": 0.0, "rest": 0.0}
         for name, entry in spans.items():
-            kind = ("products" if name.startswith("tt_gemm") else "attention" if name.startswith("tt_attention")
+            kind = ("products" if name.startswith("tt_gemm") else "attention" if name.startswith(("tt_attention", "tt_latent_attention"))
                     else "recurrence" if name.startswith(recurrent) else "rest")
             out[kind] += entry["ms"]
         return out
@@ -195,7 +211,7 @@ def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[i
         "decode": {"batch": batch, "products_ms": round(decode["products"], 4),
                    "products_frac": frac(weight_bytes_per_step(model), decode["products"], peak_bytes),
                    "attention_ms": round(decode["attention"], 4),
-                   "attention_frac": frac(kv_read_bytes_per_token(model) * mean_context * batch, decode["attention"], peak_bytes),
+                   "attention_frac": frac(kv_read_bytes(model, mean_context) * batch, decode["attention"], peak_bytes),
                    # recurrences (convolution, state update, gated norm): every state read and written once
                    "recurrence_ms": round(decode["recurrence"], 4),
                    "recurrence_frac": frac(2 * state_bytes_per_sequence(model) * batch, decode["recurrence"], peak_bytes),
@@ -268,7 +284,7 @@ def measure_decode(runtime, prompts: list[list[int]], context: int, warmup: int,
     engine.check_status()
     ms = start.elapsed_time(stop)
     mean_context = sum(lengths_before) / batch + (steps - 1) / 2.0
-    bytes_per_step = (weight_bytes_per_step(runtime.model) + kv_read_bytes_per_token(runtime.model) * mean_context * batch
+    bytes_per_step = (weight_bytes_per_step(runtime.model) + kv_read_bytes(runtime.model, mean_context) * batch
                       + 2 * state_bytes_per_sequence(runtime.model) * batch)
     result = {
         "ms_per_step": ms / steps,

@@ -60,6 +60,11 @@ class LatentAttention(Mixer):
             n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim)),
         }
 
+    @property
+    def pair_dims(self) -> tuple[int, int]:
+        """Numbers of a head's score product and of its value, for the benchmarks' FLOP model."""
+        return self.dim + self.rot_dim, self.value_dim
+
     def cache_need(self) -> KVNeed:
         return KVNeed(1, self.kv_rank + self.rot_dim, self.window, 0)       # one row per token, values read from the key rows
 
