@@ -3,8 +3,8 @@ The configurations differ from one another in every size; between them they cove
 and rotated sizes that differ, latents smaller and larger than the heads they expand into, windows shorter than a
 cache block, longer than one and none at all, a rotation of part of a retention head and of all of it and none,
 decays from fast to very slow, experts in one group and in several of which one or two stay, one choice per token and
-several, layers with and without a shared expert and without any feed-forward, a model without the pair table, and a
-model without any attention layer."""
+several, layers with and without a shared expert and without any feed-forward, a model without the pair table, a model
+without any attention layer, and one whose attention heads have the sizes that prompts expand for the tensor cores."""
 from __future__ import annotations
 
 import json
@@ -61,8 +61,23 @@ CONFIGS = {
                                                          "rot": {"dims": 16, "base": 10000.0}}},
         ],
     },
+    # heads of 64 and of 128 numbers for keys and values alike: the sizes whose prompts are expanded for the tensor-core
+    # attention kernel in bfloat16 (a window that ends inside the second block, and none)
+    "d": {
+        "architecture": "Neruzen", "vocab": 160, "width": 128, "norm": {"eps": 1e-6},
+        "embedding": {"bigram": {"buckets": 61, "mul_prev": 3, "mul_cur": 5}},
+        "layers": [
+            {"type": "latent_attention", "mlp": _moe(4, 2, 48, (2, 1), 64), "mixer": {
+                "heads": 2, "dim": 32, "rot_dim": 32, "vdim": 64, "q_rank": 40, "kv_rank": 48, "scale": 0.125, "mask": {"size": 100},
+                "rot": {"dims": 32, "base": 10000.0}}},
+            {"type": "lightning", "mlp": None, "mixer": {"heads": 2, "dim": 32, "vdim": 32, "decay": [0.9, 0.99]}},
+            {"type": "latent_attention", "mlp": None, "mixer": {
+                "heads": 3, "dim": 96, "rot_dim": 32, "vdim": 128, "q_rank": 64, "kv_rank": 72, "scale": 0.09,
+                "rot": {"dims": 32, "base": 100000.0}}},
+        ],
+    },
 }
-SEEDS = {"a": 3, "b": 4, "c": 6}
+SEEDS = {"a": 3, "b": 4, "c": 6, "d": 8}
 
 
 def shape_weights(tensors: dict[str, torch.Tensor], seed: int) -> dict[str, torch.Tensor]:

@@ -108,7 +108,7 @@ def test_prompt_in_portions(folders, name, dtype):
     judge = Judge(dtype, folder)
     engine = load(folder, dtype).new_engine(max_tokens=512, max_sequences=2)
     tokens = token_ids(CONFIGS[name]["vocab"], 190, 210)
-    for cuts in ([2, 2, 2, 1, 3, 11, 2, 41, 2, 64, 20, 40], [61, 3, 1, 1, 2, 82, 40], [16, 16, 32, 1, 85, 19, 21]):
+    for cuts in ([2, 2, 2, 1, 3, 11, 2, 41, 2, 64, 20, 40], [61, 3, 1, 1, 2, 82, 40], [16, 16, 32, 1, 85, 19, 21], [50, 140]):
         assert sum(cuts) == len(tokens)
         slot = engine.open()
         got, at = [], 0

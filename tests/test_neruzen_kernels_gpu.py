@@ -131,11 +131,12 @@ def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window
         for b in pick:
             cu_step.append(cu_step[-1] + new[b])
         out = torch.zeros(len(rows_of), heads * vdim, dtype=dtype, device=DEV)
-        part_acc = torch.zeros(len(rows_of) * heads * splits * rank, dtype=torch.float32, device=DEV) if splits > 1 else None
-        part_ml = torch.zeros(len(rows_of) * heads * splits * 2, dtype=torch.float32, device=DEV) if splits > 1 else None
+        absorbed = torch.zeros(len(rows_of) * heads * (rank + rot), dtype=torch.float32, device=DEV)
+        part_acc = torch.zeros(len(rows_of) * heads * splits * rank, dtype=torch.float32, device=DEV)
+        part_ml = torch.zeros(len(rows_of) * heads * splits * 2, dtype=torch.float32, device=DEV)
         word = status()
         api.latent_attention(q_step, w_key_d, w_value_d, pool, table[pick].contiguous(), i32(cu_step), i32([before[b] for b in pick]), len(pick),
-                             len(rows_of), heads, dim, rot, vdim, rank, inv_freq, rotary_dim, scale, window, splits, out, part_acc, part_ml, word)
+                             len(rows_of), heads, dim, rot, vdim, rank, inv_freq, rotary_dim, scale, window, splits, out, absorbed, part_acc, part_ml, word)
         assert int(word.item()) == 0
         err = (out.double().cpu() - want[rows_of]).abs().max()
         bound = (1e-5 if dtype == torch.float32 else 0.03) * max(1.0, float(want.abs().max()))
@@ -214,6 +215,18 @@ def test_routing(experts, top, groups, keep):
         dense = torch.zeros(experts, dtype=torch.float64)
         dense[ids] = w
         assert float((gates[t].double().cpu() - dense).abs().max()) <= 1e-6
+    # the same with the router's product in front, from rows and a matrix in either dtype
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(tokens, 72, generator=g).to(dtype)
+        w = (torch.randn(experts, 72, generator=g) * 0.5).to(dtype)
+        gates.fill_(-1.0)
+        api.route_rows(x.to(DEV), w.to(DEV), top, groups, keep, gates, chosen, weights)
+        scores = torch.softmax(x.double() @ w.double().T, dim=-1)
+        for t in range(tokens):
+            ids, wt = route_plain(scores[t], top, groups, keep)
+            assert chosen[t].tolist() == ids, f"token {t}"
+            assert float((weights[t].double().cpu() - wt).abs().max()) <= 1e-5
+            assert float(gates[t].sum()) == pytest.approx(1.0, abs=1e-5)
 
 
 def test_expert_columns_are_scaled_and_the_shared_ones_left():

@@ -8,11 +8,18 @@
 // divides the two latents by their root mean square (times their weights), writes the query latent for the
 // up projection, rotates k_rot by the token's position and appends [c | k_rot] to the token's cache row.
 //
-// tt_latent_attention: one warp per (token, head).  Prologue: sums the slices of the head's query, rotates its
-// rotated part, forms a_h.  Main loop: a lane per key of a tile of 32 (16-byte loads along the row), online softmax,
-// the weighted latents accumulated with lanes across the latent's numbers.  Epilogue: Wv_h times the normalised sum.
-// Keys can be cut into slices (decoding long contexts): a slice leaves (sum, maximum, denominator) in scratch memory
-// and tt_latent_merge combines the slices in order and applies Wv_h.
+// tt_latent_attention: three kernels.  (1) A block per (token, head) sums the slices of the head's query, rotates its
+// rotated part and forms a_h, threads across the latent.  (2) A warp per (token, head) and slice of the keys: a lane per
+// key of a tile of 32 (16-byte loads along the row), online softmax, the weighted latents accumulated with every lane
+// taking 16 bytes of a latent at a time; the slice leaves (sum, maximum, denominator) in scratch memory.  (3) A block per
+// (token, head) combines the slices in order and applies Wv_h, a warp per output number.
+//
+// Prompts may instead EXPAND the latents they can see into per-head keys and values for the step, laid out like blocks
+// of the ordinary cache (keys [block][head][64][dim + rot], values transposed [block][head][vdim][64]) with a table of
+// their own, so that the tensor-core attention kernels for ordinary heads run on them:
+// tt_latent_expand_plan (which blocks of which sequence the step can see, and where they go), tt_latent_gather (their
+// latents into one matrix for the product with [Wk; Wv], their shared rotated parts into every head's keys),
+// tt_latent_scatter (the product's rows into keys and transposed values) and tt_latent_queries (rotated queries).
 #include "attention_kernels.cuh"
 
 constexpr int LAT_WARPS = 4;
@@ -70,69 +77,100 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, int splits
 
 template <typename T> __device__ __forceinline__ float lat_weight(const T* p) { return tt_to_float(*p); }
 
-// window <= 0: all keys 0..pos.  window > 0: keys pos - window + 1 .. pos.
-template <typename TOut, typename TC, typename TW>
-__global__ void latent_attention_kernel(const float* __restrict__ q, int q_splits, size_t q_stride, const TW* __restrict__ w_key,
-                                        const TW* __restrict__ w_value, const TC* __restrict__ pool, const int* __restrict__ table,
+// 16 bytes of a cache row as floats: N numbers
+template <typename T> struct LatVec;
+template <> struct LatVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+};
+template <> struct LatVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+// The query a head's scores are taken with, one block per (token, head): [Wk_h^T q_plain | rotated q_rot] * scale, float32
+// [tokens][heads][rank + rot].  Threads run across the latent, so that a row of Wk_h is read side by side.
+template <typename TW>
+__global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, size_t q_stride, const TW* __restrict__ w_key,
+                                     const int* __restrict__ cu, const int* __restrict__ len_before, int sequences, int heads, int dim,
+                                     int rot, int rank, const float* __restrict__ inv_freq, int rotary_dim, float scale,
+                                     float* __restrict__ absorbed) {
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
+    int pos = 0;
+    if (rotary_dim > 0) {
+        const int b = tt_find_sequence(cu, sequences, t);
+        pos = len_before[b] + (t - cu[b]);
+    }
+    tt_pdl_wait();
+    extern __shared__ float lat_shared[];                       // dim + rot
+    const float* qsrc = q + ((size_t)t * heads + h) * (dim + rot);
+    for (int d = threadIdx.x; d < dim + rot; d += blockDim.x) {
+        float x = 0.0f;
+        for (int s = 0; s < q_splits; ++s) x += qsrc[(size_t)s * q_stride + d];
+        lat_shared[d] = x;
+    }
+    __syncthreads();
+    float* out = absorbed + ((size_t)t * heads + h) * (rank + rot);
+    const float* qr = lat_shared + dim;
+    const int half = rotary_dim >> 1;
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+        float v = qr[i];
+        if (i < rotary_dim) {
+            float sn, cs;
+            sincosf((float)pos * __ldg(inv_freq + (i < half ? i : i - half)), &sn, &cs);
+            v = i < half ? qr[i] * cs - qr[i + half] * sn : qr[i] * cs + qr[i - half] * sn;
+        }
+        out[rank + i] = v * scale;
+    }
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+        const TW* col = w_key + (size_t)h * dim * rank + r;
+        float a0 = 0.0f, a1 = 0.0f;
+        int d = 0;
+        for (; d + 2 <= dim; d += 2) {
+            a0 = fmaf(lat_weight(col + (size_t)d * rank), lat_shared[d], a0);
+            a1 = fmaf(lat_weight(col + (size_t)(d + 1) * rank), lat_shared[d + 1], a1);
+        }
+        if (d < dim) a0 = fmaf(lat_weight(col + (size_t)d * rank), lat_shared[d], a0);
+        out[r] = (a0 + a1) * scale;
+    }
+}
+
+// One warp per (token, head) and key slice.  window <= 0: all keys 0..pos.  window > 0: keys pos - window + 1 .. pos.
+// Leaves the slice's weighted sum of latents, maximum and denominator in part_acc / part_ml.
+template <typename TC>
+__global__ void latent_attention_kernel(const float* __restrict__ absorbed, const TC* __restrict__ pool, const int* __restrict__ table,
                                         int table_width, int pool_blocks, const int* __restrict__ cu,
-                                        const int* __restrict__ len_before, int sequences, int n_tokens, int heads, int dim, int rot,
-                                        int vdim, int rank, const float* __restrict__ inv_freq, int rotary_dim, float scale,
-                                        int window, int splits, TOut* __restrict__ out, float* __restrict__ part_acc,
-                                        float* __restrict__ part_ml, unsigned* status) {
+                                        const int* __restrict__ len_before, int sequences, int n_tokens, int heads, int rot, int rank,
+                                        int window, int splits, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                                        unsigned* status) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float lat_shared[];                       // per warp: rank + rot (the absorbed query), then dim
+    extern __shared__ float lat_shared[];                       // per warp: rank + rot (the absorbed query)
+    constexpr int VEC = LatVec<TC>::N, CHUNKS = LAT_MAX_RANK / VEC / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * LAT_WARPS + warp;   // (token, head)
     if (item >= (long long)n_tokens * heads) return;
-    const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+    const int t = (int)(item / heads);
     const int split = blockIdx.y;
     const int b = tt_find_sequence(cu, sequences, t);
     const int pos = len_before[b] + (t - cu[b]);
     const int* table_row = table + (size_t)b * table_width;
     const int row_len = rank + rot;
-    float* qa = lat_shared + (size_t)warp * (row_len + dim);
-    float* qp = qa + row_len;
-
-    // the head's query: dim unrotated numbers, then rot numbers of which the first rotary_dim are rotated
-    const float* qsrc = q + ((size_t)t * heads + h) * (dim + rot);
-    for (int d = lane; d < dim + rot; d += 32) {
-        float x = 0.0f;
-        for (int s = 0; s < q_splits; ++s) x += qsrc[(size_t)s * q_stride + d];
-        if (d < dim) qp[d] = x; else qa[rank + d - dim] = x;
-    }
-    __syncwarp();
-    {
-        const int half = rotary_dim >> 1;
-        float* qr = qa + rank;
-        for (int i = lane; i < half; i += 32) {
-            float sn, cs;
-            sincosf((float)pos * __ldg(inv_freq + i), &sn, &cs);
-            const float u = qr[i], v = qr[i + half];
-            qr[i] = (u * cs - v * sn) * scale;
-            qr[i + half] = (v * cs + u * sn) * scale;
-        }
-        for (int i = rotary_dim + lane; i < rot; i += 32) qr[i] *= scale;
-    }
-    // a = Wk_h^T q (rank numbers): lanes across the latent, so that a row of Wk_h is read side by side
-    float acc[LAT_MAX_RANK / 32];
-#pragma unroll
-    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] = 0.0f;
-    for (int d = 0; d < dim; ++d) {
-        const float qd = qp[d];
-        const TW* wrow = w_key + ((size_t)h * dim + d) * rank;
-#pragma unroll
-        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-            const int r = lane + 32 * i;
-            if (r < rank) acc[i] = fmaf(lat_weight(wrow + r), qd, acc[i]);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-        const int r = lane + 32 * i;
-        if (r < rank) qa[r] = acc[i] * scale;
-        acc[i] = 0.0f;
-    }
+    float* qa = lat_shared + (size_t)warp * row_len;
+    const float* src = absorbed + (size_t)item * row_len;
+    for (int d = lane; d < row_len; d += 32) qa[d] = src[d];
     __syncwarp();
 
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -141,7 +179,13 @@ __global__ void latent_attention_kernel(const float* __restrict__ q, int q_split
     per = (per + 31) & ~31;
     const int begin = first + split * per;
     const int end = min(begin + per, pos + 1);
+    const bool vec = (rank % VEC) == 0 && (row_len % VEC) == 0;  // a lane takes 16 bytes of a latent at a time
 
+    float acc[CHUNKS][VEC];                                     // vec: numbers (lane + 32 c) * VEC + e; else lane + 32 (c * VEC + e)
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[c][e] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;
     for (int base = begin; base < end; base += 32) {
         const int key = base + lane;
@@ -159,100 +203,84 @@ __global__ void latent_attention_kernel(const float* __restrict__ q, int q_split
         l_run = l_run * corr + tt_warp_sum(p);
         m_run = m_new;
 #pragma unroll
-        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] *= corr;
+        for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[c][e] *= corr;
         const int count = min(32, end - base);
         for (int j = 0; j < count; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long oj = __shfl_sync(0xffffffffu, off, j);
             if (oj < 0) continue;
             const TC* crow = pool + oj;                         // the key's latent is also its value
+            if (vec) {
 #pragma unroll
-            for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-                const int r = lane + 32 * i;
-                if (r < rank) acc[i] = fmaf(pj, tt_to_float(crow[r]), acc[i]);
+                for (int c = 0; c < CHUNKS; ++c) {
+                    const int r = (lane + 32 * c) * VEC;
+                    if (r < rank) {
+                        float v[VEC];
+                        LatVec<TC>::load(crow + r, v);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) acc[c][e] = fmaf(pj, v[e], acc[c][e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        const int r = lane + 32 * (c * VEC + e);
+                        if (r < rank) acc[c][e] = fmaf(pj, tt_to_float(crow[r]), acc[c][e]);
+                    }
             }
         }
     }
-
-    if (splits > 1) {
-        const size_t slot = ((size_t)t * heads + h) * splits + split;
+    const size_t slot = (size_t)item * splits + split;
 #pragma unroll
-        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-            const int r = lane + 32 * i;
-            if (r < rank) part_acc[slot * rank + r] = acc[i];
-        }
-        if (lane == 0) {
-            part_ml[slot * 2] = m_run;
-            part_ml[slot * 2 + 1] = l_run;
-        }
-        return;
-    }
-    // the head's output: Wv_h times the normalised sum of latents
-    const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-    __syncwarp();
+    for (int c = 0; c < CHUNKS; ++c)
 #pragma unroll
-    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-        const int r = lane + 32 * i;
-        if (r < rank) qa[r] = acc[i] * inv;
-    }
-    __syncwarp();
-    for (int v0 = 0; v0 < vdim; v0 += 32) {
-        const int v = v0 + lane;
-        float o = 0.0f;
-        if (v < vdim) {
-            const TW* wrow = w_value + ((size_t)h * vdim + v) * rank;
-            for (int r = 0; r < rank; ++r) o = fmaf(lat_weight(wrow + r), qa[r], o);
-            out[((size_t)t * heads + h) * vdim + v] = tt_from_float<TOut>(o);
+        for (int e = 0; e < VEC; ++e) {
+            const int r = vec ? (lane + 32 * c) * VEC + e : lane + 32 * (c * VEC + e);
+            if (r < rank) part_acc[slot * rank + r] = acc[c][e];
         }
+    if (lane == 0) {
+        part_ml[slot * 2] = m_run;
+        part_ml[slot * 2 + 1] = l_run;
     }
 }
 
-// Combines the key slices of one (token, head) in slice order and applies Wv_h.  One warp per row.
+// One block per (token, head): combines the key slices in slice order into the normalised sum of latents, then a warp per
+// output number takes Wv_h's row times it, lanes across the latent.
 template <typename TOut, typename TW>
-__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int splits, int rank,
-                                    int vdim, int heads, long long rows, const TW* __restrict__ w_value, TOut* __restrict__ out) {
+__global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int splits, int rank,
+                                           int vdim, int heads, const TW* __restrict__ w_value, TOut* __restrict__ out) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float lat_shared[];                       // per warp: rank
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * LAT_WARPS + warp;
-    if (row >= rows) return;
+    extern __shared__ float lat_shared[];                       // rank
+    const size_t row = blockIdx.x;
     const int h = (int)(row % heads);
-    float* o_lat = lat_shared + (size_t)warp * rank;
-    const float* ml = part_ml + (size_t)row * splits * 2;
+    const float* ml = part_ml + row * splits * 2;
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
     float l = 0.0f;
-    float acc[LAT_MAX_RANK / 32];
-#pragma unroll
-    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = ml[2 * s];
-        if (ms == -INFINITY) continue;
-        const float w = expf(ms - m);
-        l += ml[2 * s + 1] * w;
-        const float* a = part_acc + ((size_t)row * splits + s) * rank;
-#pragma unroll
-        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-            const int r = lane + 32 * i;
-            if (r < rank) acc[i] = fmaf(a[r], w, acc[i]);
-        }
-    }
+    for (int s = 0; s < splits; ++s)
+        if (ml[2 * s] != -INFINITY) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-#pragma unroll
-    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
-        const int r = lane + 32 * i;
-        if (r < rank) o_lat[r] = acc[i] * inv;
-    }
-    __syncwarp();
-    for (int v0 = 0; v0 < vdim; v0 += 32) {
-        const int v = v0 + lane;
-        if (v < vdim) {
-            float o = 0.0f;
-            const TW* wrow = w_value + ((size_t)h * vdim + v) * rank;
-            for (int r = 0; r < rank; ++r) o = fmaf(lat_weight(wrow + r), o_lat[r], o);
-            out[(size_t)row * vdim + v] = tt_from_float<TOut>(o);
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) acc = fmaf(part_acc[(row * splits + s) * rank + r], expf(ms - m), acc);
         }
+        lat_shared[r] = acc * inv;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int v = warp; v < vdim; v += warps) {
+        const TW* wrow = w_value + ((size_t)h * vdim + v) * rank;
+        float o = 0.0f;
+        for (int r = lane; r < rank; r += 32) o = fmaf(lat_weight(wrow + r), lat_shared[r], o);
+        o = tt_warp_sum(o);
+        if (lane == 0) out[row * vdim + v] = tt_from_float<TOut>(o);
     }
 }
 
@@ -278,23 +306,193 @@ extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_str
                                    int weight_dtype, const void* pool, int act_dtype, const int* table, int table_width, int pool_blocks,
                                    const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int dim, int rot,
                                    int vdim, int rank, const float* inv_freq, int rotary_dim, float scale, int window, int splits,
-                                   void* out, float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+                                   void* out, float* absorbed, float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rank > LAT_MAX_RANK || rank + rot > LAT_MAX_ROW || dim <= 0 || dim > LAT_MAX_DIM || vdim <= 0 || splits < 1 ||
-        splits > 65535 || rotary_dim > rot || (rotary_dim & 1) || (splits > 1 && (!part_acc || !part_ml)))
+        splits > 65535 || rotary_dim > rot || (rotary_dim & 1) || !absorbed || !part_acc || !part_ml)
         return (int)cudaErrorInvalidValue;
     const long long rows = (long long)n_tokens * heads;
     const long long blocks = (rows + LAT_WARPS - 1) / LAT_WARPS;
-    if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
-    const size_t shared = (size_t)LAT_WARPS * (rank + rot + dim) * sizeof(float);
+    if (rows > 2147483647LL) return (int)cudaErrorInvalidValue;
+    const size_t shared = (size_t)LAT_WARPS * (rank + rot) * sizeof(float);
     const dim3 grid((unsigned)blocks, splits), block(LAT_WARPS * 32);
-#define TT_ATT(TA, TW) tt_launch_pdl(latent_attention_kernel<TA, TA, TW>, grid, block, shared, stream, q, q_splits, (size_t)q_stride, (const TW*)w_key, (const TW*)w_value, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, dim, rot, vdim, rank, inv_freq, rotary_dim, scale, window, splits, (TA*)out, part_acc, part_ml, status)
-#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_kernel<TA, TW>, dim3((unsigned)blocks), block, (size_t)LAT_WARPS * rank * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, rows, (const TW*)w_value, (TA*)out)
-    if (act_dtype == TT_F32 && weight_dtype == TT_F32) { TT_ATT(float, float); if (splits > 1) TT_MERGE(float, float); }
-    else if (act_dtype == TT_F32) { TT_ATT(float, __nv_bfloat16); if (splits > 1) TT_MERGE(float, __nv_bfloat16); }
-    else if (weight_dtype == TT_F32) { TT_ATT(__nv_bfloat16, float); if (splits > 1) TT_MERGE(__nv_bfloat16, float); }
-    else { TT_ATT(__nv_bfloat16, __nv_bfloat16); if (splits > 1) TT_MERGE(__nv_bfloat16, __nv_bfloat16); }
+#define TT_ABSORB(TW) tt_launch_pdl(latent_absorb_kernel<TW>, dim3((unsigned)rows), dim3(128), (size_t)(dim + rot) * sizeof(float), stream, q, q_splits, (size_t)q_stride, (const TW*)w_key, cu, len_before, sequences, heads, dim, rot, rank, inv_freq, rotary_dim, scale, absorbed)
+#define TT_ATT(TA) tt_launch_pdl(latent_attention_kernel<TA>, grid, block, shared, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
+#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_expand_kernel<TA, TW>, dim3((unsigned)rows), dim3(128), (size_t)rank * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, (const TW*)w_value, (TA*)out)
+    if (weight_dtype == TT_F32) TT_ABSORB(float); else TT_ABSORB(__nv_bfloat16);
+    if (act_dtype == TT_F32) TT_ATT(float); else TT_ATT(__nv_bfloat16);
+    if (act_dtype == TT_F32 && weight_dtype == TT_F32) TT_MERGE(float, float);
+    else if (act_dtype == TT_F32) TT_MERGE(float, __nv_bfloat16);
+    else if (weight_dtype == TT_F32) TT_MERGE(__nv_bfloat16, float);
+    else TT_MERGE(__nv_bfloat16, __nv_bfloat16);
+#undef TT_ABSORB
 #undef TT_ATT
 #undef TT_MERGE
+    TT_LAUNCH_CHECK();
+}
+
+
+// ------------------------------------------------------------------------------------
+// Expansion of the visible latents of a step of prompts (see the top of the file).
+// plan: int32 [sequences + 1] first temporary block of every sequence (and their total), then [sequences] the first
+// cache block (position / 64) each sequence's temporary blocks stand for.
+// ------------------------------------------------------------------------------------
+__global__ void latent_expand_plan_kernel(const int* __restrict__ cu, const int* __restrict__ len_before, int sequences, int window,
+                                          int table_width, int bound_blocks, int* __restrict__ plan, int* __restrict__ table_tmp,
+                                          unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int b = 0; b < sequences; ++b) {
+            const int before = len_before[b], after = before + cu[b + 1] - cu[b];
+            const int first_pos = (window > 0 && before - window + 1 > 0) ? before - window + 1 : 0;   // oldest key the step's first token sees
+            const int first_block = first_pos / TT_BLOCK_TOKENS;
+            int blocks = (after + TT_BLOCK_TOKENS - 1) / TT_BLOCK_TOKENS - first_block;
+            if (at + blocks > bound_blocks) {                  // cannot happen with the bound the host computes
+                atomicOr(status, TT_STATUS_BAD_SHAPE);
+                blocks = bound_blocks - at;
+            }
+            plan[b] = at;
+            plan[sequences + 1 + b] = first_block;
+            at += blocks;
+        }
+        plan[sequences] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < sequences * table_width; e += blockDim.x) {
+        const int b = e / table_width, i = e - b * table_width;
+        const int first_block = plan[sequences + 1 + b], blocks = plan[b + 1] - plan[b];
+        table_tmp[e] = (i >= first_block && i < first_block + blocks) ? plan[b] + (i - first_block) : -1;
+    }
+}
+
+// One block per row of the temporary blocks (block * 64 + token).  x: [rows][rank]; keys: [block][heads][64][dim + rot].
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __restrict__ table, int table_width, int pool_blocks,
+                                     const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
+                                     const int* __restrict__ plan, int heads, int dim, int rot, int rank, T* __restrict__ x,
+                                     T* __restrict__ keys) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int row = blockIdx.x, tb = row / TT_BLOCK_TOKENS, r = row - tb * TT_BLOCK_TOKENS;
+    long long off = -1;
+    if (tb < plan[sequences]) {
+        const int b = tt_find_sequence(plan, sequences, tb);   // plan[b] <= tb < plan[b + 1]; sequences without blocks are skipped by the search
+        const int pos = (plan[sequences + 1 + b] + tb - plan[b]) * TT_BLOCK_TOKENS + r;
+        if (pos < len_before[b] + cu[b + 1] - cu[b])
+            off = tt_cache_offset(table + (size_t)b * table_width, pos, 0, 1, rank + rot, pool_blocks, nullptr);   // a block the window gave back: zeros
+    }
+    const T zero = tt_from_float<T>(0.0f);
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) x[(size_t)row * rank + j] = off >= 0 ? pool[off + j] : zero;
+    const int hd = dim + rot;
+    for (int e = threadIdx.x; e < heads * rot; e += blockDim.x) {
+        const int h = e / rot, j = e - h * rot;
+        keys[(((size_t)tb * heads + h) * TT_BLOCK_TOKENS + r) * hd + dim + j] = off >= 0 ? pool[off + rank + j] : zero;
+    }
+}
+
+// y: float32 partial sums [splits][rows][heads * dim + heads * vdim] of x [Wk; Wv]^T.  One block per temporary block and
+// head: the unrotated key parts go out row by row, the values through shared memory so that a value number's 64 tokens
+// are written side by side.
+template <typename T>
+__global__ void latent_scatter_kernel(const float* __restrict__ y, int splits, size_t split_stride, int heads, int dim, int rot,
+                                      int vdim, T* __restrict__ keys, T* __restrict__ values) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float lat_shared[];                       // [64][vdim + 1]
+    const int tb = blockIdx.x / heads, h = blockIdx.x - tb * heads;
+    const int cols = heads * (dim + vdim), hd = dim + rot;
+    const float* base = y + (size_t)tb * TT_BLOCK_TOKENS * cols;
+    for (int e = threadIdx.x; e < TT_BLOCK_TOKENS * dim; e += blockDim.x) {
+        const int r = e / dim, d = e - r * dim;
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += base[(size_t)s * split_stride + (size_t)r * cols + h * dim + d];
+        keys[(((size_t)tb * heads + h) * TT_BLOCK_TOKENS + r) * hd + d] = tt_from_float<T>(v);
+    }
+    for (int e = threadIdx.x; e < TT_BLOCK_TOKENS * vdim; e += blockDim.x) {
+        const int r = e / vdim, d = e - r * vdim;
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += base[(size_t)s * split_stride + (size_t)r * cols + heads * dim + h * vdim + d];
+        lat_shared[r * (vdim + 1) + d] = v;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < TT_BLOCK_TOKENS * vdim; e += blockDim.x) {
+        const int d = e / TT_BLOCK_TOKENS, r = e - d * TT_BLOCK_TOKENS;
+        values[(((size_t)tb * heads + h) * vdim + d) * TT_BLOCK_TOKENS + r] = tt_from_float<T>(lat_shared[r * (vdim + 1) + d]);
+    }
+}
+
+// q: float32 partial sums [splits][tokens][heads * (dim + rot)]; out: the same numbers in T with each head's last rot
+// numbers rotated by the token's position (the first rotary_dim of them, halves paired).
+template <typename T>
+__global__ void latent_queries_kernel(const float* __restrict__ q, int splits, size_t split_stride, int heads, int dim, int rot,
+                                      const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ cu,
+                                      const int* __restrict__ len_before, int sequences, T* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    tt_pdl_wait();
+    const int hd = dim + rot, half = rotary_dim >> 1;
+    const float* row = q + (size_t)t * heads * hd;
+    for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
+        const int i = e % hd - dim;                             // index inside the rotated part, negative in front of it
+        float x = 0.0f;
+        for (int s = 0; s < splits; ++s) x += row[(size_t)s * split_stride + e];
+        if (i >= 0 && i < rotary_dim) {
+            const int pair = i < half ? e + half : e - half;
+            float other = 0.0f;
+            for (int s = 0; s < splits; ++s) other += row[(size_t)s * split_stride + pair];
+            float sn, cs;
+            sincosf((float)pos * __ldg(inv_freq + (i < half ? i : i - half)), &sn, &cs);
+            x = i < half ? x * cs - other * sn : x * cs + other * sn;
+        }
+        out[(size_t)t * heads * hd + e] = tt_from_float<T>(x);
+    }
+}
+
+extern "C" int tt_latent_expand_plan(const int* cu, const int* len_before, int sequences, int window, int table_width, int bound_blocks,
+                                     int* plan, int* table_tmp, unsigned* status, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    tt_launch_pdl(latent_expand_plan_kernel, dim3(1), dim3(256), 0, stream, cu, len_before, sequences, window, table_width, bound_blocks, plan,
+                  table_tmp, status);
+    TT_LAUNCH_CHECK();
+}
+
+extern "C" int tt_latent_gather(const void* pool, int dtype, const int* table, int table_width, int pool_blocks, const int* cu,
+                                const int* len_before, int sequences, const int* plan, int bound_blocks, int heads, int dim, int rot,
+                                int rank, void* x, void* keys, cudaStream_t stream) {
+    if (bound_blocks <= 0) return 0;
+    const dim3 grid((unsigned)bound_blocks * TT_BLOCK_TOKENS), block(128);
+    if (dtype == TT_F32)
+        tt_launch_pdl(latent_gather_kernel<float>, grid, block, 0, stream, (const float*)pool, table, table_width, pool_blocks, cu, len_before, sequences, plan, heads, dim, rot, rank, (float*)x, (float*)keys);
+    else
+        tt_launch_pdl(latent_gather_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)pool, table, table_width, pool_blocks, cu, len_before, sequences, plan, heads, dim, rot, rank, (__nv_bfloat16*)x, (__nv_bfloat16*)keys);
+    TT_LAUNCH_CHECK();
+}
+
+extern "C" int tt_latent_scatter(const float* y, int splits, long long split_stride, int bound_blocks, int heads, int dim, int rot, int vdim,
+                                 void* keys, void* values, int dtype, cudaStream_t stream) {
+    if (bound_blocks <= 0) return 0;
+    const size_t shared = (size_t)TT_BLOCK_TOKENS * (vdim + 1) * sizeof(float);
+    if (shared > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const dim3 grid((unsigned)bound_blocks * heads), block(256);
+    if (dtype == TT_F32)
+        tt_launch_pdl(latent_scatter_kernel<float>, grid, block, shared, stream, y, splits, (size_t)split_stride, heads, dim, rot, vdim, (float*)keys, (float*)values);
+    else
+        tt_launch_pdl(latent_scatter_kernel<__nv_bfloat16>, grid, block, shared, stream, y, splits, (size_t)split_stride, heads, dim, rot, vdim, (__nv_bfloat16*)keys, (__nv_bfloat16*)values);
+    TT_LAUNCH_CHECK();
+}
+
+extern "C" int tt_latent_queries(const float* q, int splits, long long split_stride, int heads, int dim, int rot, const float* inv_freq,
+                                 int rotary_dim, const int* cu, const int* len_before, int sequences, int n_tokens, void* out, int dtype,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rotary_dim > rot || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+    if (dtype == TT_F32)
+        tt_launch_pdl(latent_queries_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, heads, dim, rot, inv_freq, rotary_dim, cu, len_before, sequences, (float*)out);
+    else
+        tt_launch_pdl(latent_queries_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, heads, dim, rot, inv_freq, rotary_dim, cu, len_before, sequences, (__nv_bfloat16*)out);
     TT_LAUNCH_CHECK();
 }

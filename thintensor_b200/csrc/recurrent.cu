@@ -454,7 +454,7 @@ __global__ void linear_attention_prepare_kernel(const float* __restrict__ proj, 
     const float* row = proj + (size_t)t * cols;
     float* out = vkq + (size_t)t * (hv + 2 * qk);
     const int half = rotary_dim >> 1;
-    for (int j = threadIdx.x; j < 2 * qk + hv; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < 2 * qk + hv; j += gridDim.y * blockDim.x) {
         float x = rec_sum_slices(row + j, splits, split_stride);
         if (activation) x = rec_silu(x);
         if (j >= 2 * qk) {                                       // v
@@ -481,7 +481,9 @@ extern "C" int tt_linear_attention_prepare(const float* proj, int splits, long l
                                            const int* cu, const int* len_before, int sequences, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || 2 * heads * D + heads * V > cols) return (int)cudaErrorInvalidValue;
-    tt_launch_pdl(linear_attention_prepare_kernel, dim3(n_tokens), dim3(256), 0, stream, proj, splits, (size_t)split_stride, cols, heads, D,
+    const int total = 2 * heads * D + heads * V;
+    const int tiles = n_tokens >= 1024 ? 1 : (total + 255) / 256 < 32 ? (total + 255) / 256 : 32;     // few tokens: a token's columns over several blocks
+    tt_launch_pdl(linear_attention_prepare_kernel, dim3(n_tokens, tiles), dim3(256), 0, stream, proj, splits, (size_t)split_stride, cols, heads, D,
                   V, activation, inv_freq, rotary_dim, k_scale, vkq, cu, len_before, sequences);
     TT_LAUNCH_CHECK();
 }

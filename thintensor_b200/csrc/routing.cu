@@ -7,6 +7,8 @@
 // the chosen experts and weights ([tokens][top]) and the same as a dense table ([tokens][experts], zero where an
 // expert is not chosen).
 //
+// tt_route_rows: the same with the router's product in front, from the token's row and the router's matrix.
+//
 // tt_scale_expert_columns: act[t][e * width + j] *= gates[t][e] for the first experts * width columns of act (the
 // columns behind them, a shared expert's, stay as they are).
 #include "common.cuh"
@@ -24,15 +26,11 @@ __device__ __forceinline__ void route_argmax(float& value, int& index) {
     }
 }
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, int splits, size_t split_stride, int n_tokens, int experts,
-                                  int top, int groups, int keep, float* __restrict__ gates, int* __restrict__ chosen,
-                                  float* __restrict__ weights) {
-    tt_pdl_launch_dependents();
-    tt_pdl_wait();
-    __shared__ float group_best[ROUTE_WARPS][32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * ROUTE_WARPS + warp;
-    if (t >= n_tokens) return;
+// One warp routes token t from its logits (`splits` partial sums `split_stride` apart); group_best: 32 floats of the warp's own.
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int splits, size_t split_stride, int t, int experts,
+                                            int top, int groups, int keep, float* __restrict__ gates, int* __restrict__ chosen,
+                                            float* __restrict__ weights, float* group_best_row) {
+    const int lane = threadIdx.x & 31;
     constexpr int PER = ROUTE_MAX_EXPERTS / 32;
     float s[PER];                                               // expert lane + 32 * i
     float m = -INFINITY;
@@ -42,7 +40,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int splits, 
         s[i] = -INFINITY;
         if (e < experts) {
             float z = 0.0f;
-            for (int k = 0; k < splits; ++k) z += logits[(size_t)k * split_stride + (size_t)t * experts + e];
+            for (int k = 0; k < splits; ++k) z += logits[(size_t)k * split_stride + e];
             s[i] = z;
             m = fmaxf(m, z);
         }
@@ -72,12 +70,12 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int splits, 
                 if (e < experts && e / size == g) best = fmaxf(best, s[i]);
             }
             best = tt_warp_max(best);
-            if (lane == 0) group_best[warp][g] = best;
+            if (lane == 0) group_best_row[g] = best;
         }
         __syncwarp();
         kept = 0u;
         for (int round = 0; round < keep; ++round) {
-            float v = (lane < groups && !((kept >> lane) & 1u)) ? group_best[warp][lane] : -2.0f;
+            float v = (lane < groups && !((kept >> lane) & 1u)) ? group_best_row[lane] : -2.0f;
             int g = lane;
             route_argmax(v, g);
             kept |= 1u << g;
@@ -116,6 +114,49 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int splits, 
     }
 }
 
+__global__ void route_topk_kernel(const float* __restrict__ logits, int splits, size_t split_stride, int n_tokens, int experts,
+                                  int top, int groups, int keep, float* __restrict__ gates, int* __restrict__ chosen,
+                                  float* __restrict__ weights) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    __shared__ float group_best[ROUTE_WARPS][32];
+    const int warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= n_tokens) return;
+    route_token(logits + (size_t)t * experts, splits, split_stride, t, experts, top, groups, keep, gates, chosen, weights, group_best[warp]);
+}
+
+// The router's product and the routing in one kernel, one block per token: the token's row goes to shared memory as
+// float32, every warp takes experts in turn (lanes across the row, float32 sums), and the first warp then routes the token
+// from the logits in shared memory.
+template <typename TX, typename TW>
+__global__ void route_rows_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int hidden, int n_tokens, int experts, int top,
+                                  int groups, int keep, float* __restrict__ gates, int* __restrict__ chosen,
+                                  float* __restrict__ weights) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float route_shared[];                     // hidden, then experts, then 32
+    float* logits = route_shared + hidden;
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) route_shared[j] = tt_to_float(x[(size_t)t * hidden + j]);
+    __syncthreads();
+    for (int e = warp; e < experts; e += warps) {
+        const TW* row = w + (size_t)e * hidden;
+        float a0 = 0.0f, a1 = 0.0f;
+        int j = lane;
+        for (; j + 32 < hidden; j += 64) {
+            a0 = fmaf(tt_to_float(row[j]), route_shared[j], a0);
+            a1 = fmaf(tt_to_float(row[j + 32]), route_shared[j + 32], a1);
+        }
+        if (j < hidden) a0 = fmaf(tt_to_float(row[j]), route_shared[j], a0);
+        const float z = tt_warp_sum(a0 + a1);
+        if (lane == 0) logits[e] = z;
+    }
+    __syncthreads();
+    if (warp == 0) route_token(logits, 1, 0, t, experts, top, groups, keep, gates, chosen, weights, logits + experts);
+}
+
 template <typename T>
 __global__ void scale_expert_columns_kernel(T* __restrict__ act, int row_stride, int width, int experts,
                                             const float* __restrict__ gates, long long total) {
@@ -142,11 +183,58 @@ extern "C" int tt_route_topk(const float* logits, int splits, long long split_st
     TT_LAUNCH_CHECK();
 }
 
+// the same, 16 bytes a thread (width and row_stride are multiples of N numbers)
+template <typename T, int N>
+__global__ void scale_expert_columns_vec_kernel(T* __restrict__ act, int row_stride, int width, int experts,
+                                                const float* __restrict__ gates, long long total) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * N;
+    if (i >= total) return;
+    const int per_row = experts * width;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row);
+    const float g = gates[t * experts + c / width];
+    uint4* p = reinterpret_cast<uint4*>(act + t * row_stride + c);
+    uint4 raw = *p;
+    T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int e = 0; e < N; ++e) v[e] = tt_from_float<T>(tt_to_float(v[e]) * g);
+    *p = raw;
+}
+
+extern "C" int tt_route_rows(const void* x, int x_dtype, const void* w, int w_dtype, int hidden, int n_tokens, int experts, int top,
+                             int groups, int keep, float* gates, int* chosen, float* weights, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (experts <= 0 || experts > ROUTE_MAX_EXPERTS || top < 1 || top > 32 || top > experts || groups < 1 || groups > 32 ||
+        experts % groups || keep < 1 || keep > groups)
+        return (int)cudaErrorInvalidValue;
+    const size_t shared = (size_t)(hidden + experts + 32) * sizeof(float);
+    if (shared > 48 * 1024) return (int)cudaErrorInvalidValue;
+#define TT_ROUTE(TX, TW) tt_launch_pdl(route_rows_kernel<TX, TW>, dim3(n_tokens), dim3(128), shared, stream, (const TX*)x, (const TW*)w, hidden, n_tokens, experts, top, groups, keep, gates, chosen, weights)
+    if (x_dtype == TT_F32 && w_dtype == TT_F32) TT_ROUTE(float, float);
+    else if (x_dtype == TT_F32) TT_ROUTE(float, __nv_bfloat16);
+    else if (w_dtype == TT_F32) TT_ROUTE(__nv_bfloat16, float);
+    else TT_ROUTE(__nv_bfloat16, __nv_bfloat16);
+#undef TT_ROUTE
+    TT_LAUNCH_CHECK();
+}
+
 extern "C" int tt_scale_expert_columns(void* act, int dtype, int n_tokens, int row_stride, int width, int experts, const float* gates,
                                        cudaStream_t stream) {
     const long long total = (long long)n_tokens * experts * width;
     if (total <= 0) return 0;
     const int threads = 256;
+    const int n = dtype == TT_F32 ? 4 : 8;
+    if (width % n == 0 && row_stride % n == 0 && ((uintptr_t)act & 15) == 0) {
+        const long long blocks = (total / n + threads - 1) / threads;
+        if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
+        if (dtype == TT_F32)
+            tt_launch_pdl(scale_expert_columns_vec_kernel<float, 4>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)act, row_stride, width, experts, gates, total);
+        else
+            tt_launch_pdl(scale_expert_columns_vec_kernel<__nv_bfloat16, 8>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)act, row_stride, width, experts, gates, total);
+        TT_LAUNCH_CHECK();
+    }
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
     if (dtype == TT_F32)

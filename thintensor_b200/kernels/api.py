@@ -698,14 +698,15 @@ def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int, q_weigh
 def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor, pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                      len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, dim: int, rot: int, vdim: int, rank: int,
                      inv_freq: torch.Tensor, rotary_dim: int, scale: float, window: int, splits: int, out: torch.Tensor,
-                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
+                     absorbed: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, status: torch.Tensor) -> None:
     """Causal softmax attention over a latent cache.  ``q``: float32 partial sums ``[slices, tokens, heads * (dim + rot)]`` of
     the queries (per head ``dim`` unrotated numbers, then ``rot`` of which the first ``rotary_dim`` are rotated here);
     ``w_key`` ``[heads * dim, rank]`` and ``w_value`` ``[heads * vdim, rank]`` expand a latent into a head's keys and values;
     ``pool`` ``[blocks, 1, 64, rank + rot]`` holds per token the latent and the rotated key part all heads share.  Score of
     query i and key j: ``(q_plain . w_key_h c_j + q_rot . k_rot_j) * scale`` for ``0 <= i - j < window`` (``window`` 0: every
-    earlier key); ``out`` ``[tokens, heads * vdim]``.  ``splits`` > 1 cuts the keys into slices whose partial results go
-    through ``part_acc`` ``[tokens * heads * splits * rank]`` and ``part_ml`` ``[tokens * heads * splits * 2]``."""
+    earlier key); ``out`` ``[tokens, heads * vdim]``.  Scratch memory, all float32: ``absorbed`` ``[tokens * heads * (rank +
+    rot)]`` for the queries with ``w_key`` folded in; ``part_acc`` ``[tokens * heads * splits * rank]`` and ``part_ml``
+    ``[tokens * heads * splits * 2]`` for the ``splits`` slices the keys are cut into."""
     _need(inv_freq, torch.float32, "inverse frequencies")
     if rank > LATENT_MAX_RANK or rank + rot > LATENT_MAX_ROW or dim > LATENT_MAX_DIM:
         raise KernelError(f"latent attention takes latents of up to {LATENT_MAX_RANK}, rows of up to {LATENT_MAX_ROW} and "
@@ -716,19 +717,72 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
             or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot) or pool.dtype != out.dtype
             or tuple(out.shape) != (n_tokens, heads * vdim) or not out.is_contiguous()):
         raise KernelError("latent_attention: shapes do not fit the sizes")
-    if splits > 1:
-        _need(part_acc, torch.float32, "slice sums")
-        _need(part_ml, torch.float32, "slice maxima")
-        if part_acc.numel() < n_tokens * heads * splits * rank or part_ml.numel() < n_tokens * heads * splits * 2:
-            raise KernelError("latent_attention: scratch memory for the key slices is too small")
+    for t, name in ((absorbed, "folded queries"), (part_acc, "slice sums"), (part_ml, "slice maxima")):
+        _need(t, torch.float32, name)
+    if (absorbed.numel() < n_tokens * heads * (rank + rot) or part_acc.numel() < n_tokens * heads * splits * rank
+            or part_ml.numel() < n_tokens * heads * splits * 2):
+        raise KernelError("latent_attention: scratch memory is too small")
     fn = _fn("latent_attention", "tt_latent_attention", [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                                          c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                          c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                         c_void_p])
+                                                         c_void_p, c_void_p])
     _check(fn(p, q_splits, q_stride, _ptr(w_key), _ptr(w_value), dtype_code(w_key.dtype), _ptr(pool), dtype_code(out.dtype), _ptr(table),
               table.shape[1], pool.shape[0], _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, dim, rot, vdim, rank, _ptr(inv_freq),
-              rotary_dim, scale, window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()),
-           "latent_attention", 2 if splits > 1 else 1)
+              rotary_dim, scale, window, splits, _ptr(out), _ptr(absorbed), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()),
+           "latent_attention", 3)
+
+
+def latent_expand(pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor, sequences: int, window: int,
+                  bound_blocks: int, heads: int, dim: int, rot: int, rank: int, plan: torch.Tensor, table_tmp: torch.Tensor,
+                  x: torch.Tensor, keys: torch.Tensor, status: torch.Tensor) -> None:
+    """First half of expanding the latents a step of prompts can see into per-head keys and values laid out like cache blocks:
+    ``table_tmp`` (int32 ``[sequences, table width]``) names, for every sequence, the temporary block that stands for each
+    cache block the step reads (-1 elsewhere); ``x`` ``[bound_blocks * 64, rank]`` receives those blocks' latents (zero rows where
+    there is no token) for the product with ``[w_key; w_value]``, and ``keys`` ``[bound_blocks, heads, 64, dim + rot]`` the
+    shared rotated part behind every head's ``dim`` numbers.  ``plan``: int32 scratch ``[2 * sequences + 1]``.
+    ``bound_blocks`` must be at least the blocks the step can see (the kernel flags a bad shape otherwise)."""
+    _need(plan, torch.int32, "expansion plan")
+    _need(table_tmp, torch.int32, "temporary table")
+    if (plan.numel() < 2 * sequences + 1 or tuple(table_tmp.shape) != tuple(table.shape) or tuple(x.shape) != (bound_blocks * BLOCK_TOKENS, rank)
+            or tuple(keys.shape) != (bound_blocks, heads, BLOCK_TOKENS, dim + rot) or not (pool.dtype == x.dtype == keys.dtype)
+            or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot) or not x.is_contiguous() or not keys.is_contiguous()):
+        raise KernelError("latent_expand: shapes do not fit the sizes")
+    fn = _fn("latent_attention", "tt_latent_expand_plan", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(cu), _ptr(len_before), sequences, window, table.shape[1], bound_blocks, _ptr(plan), _ptr(table_tmp), _ptr(status), _stream()),
+           "latent_expand_plan")
+    fn = _fn("latent_attention", "tt_latent_gather", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(pool), dtype_code(pool.dtype), _ptr(table), table.shape[1], pool.shape[0], _ptr(cu), _ptr(len_before), sequences, _ptr(plan),
+              bound_blocks, heads, dim, rot, rank, _ptr(x), _ptr(keys), _stream()), "latent_gather")
+
+
+def latent_scatter(y: torch.Tensor, heads: int, dim: int, rot: int, vdim: int, keys: torch.Tensor, values: torch.Tensor) -> None:
+    """Second half: ``y``, the float32 partial sums ``[slices, bound_blocks * 64, heads * dim + heads * vdim]`` of the gathered
+    latents times ``[w_key; w_value]``, into the first ``dim`` numbers of every head's keys and into ``values``
+    ``[bound_blocks, heads, vdim, 64]`` (transposed inside a block, like the cache's)."""
+    p, splits, stride, cols = _projection(y)
+    blocks = keys.shape[0]
+    if (cols != heads * (dim + vdim) or y.shape[1] != blocks * BLOCK_TOKENS or tuple(keys.shape) != (blocks, heads, BLOCK_TOKENS, dim + rot)
+            or tuple(values.shape) != (blocks, heads, vdim, BLOCK_TOKENS) or keys.dtype != values.dtype
+            or not keys.is_contiguous() or not values.is_contiguous()):
+        raise KernelError("latent_scatter: shapes do not fit the sizes")
+    fn = _fn("latent_attention", "tt_latent_scatter", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                                       c_void_p])
+    _check(fn(p, splits, stride, blocks, heads, dim, rot, vdim, _ptr(keys), _ptr(values), dtype_code(keys.dtype), _stream()), "latent_scatter")
+
+
+def latent_queries(q: torch.Tensor, heads: int, dim: int, rot: int, inv_freq: torch.Tensor, rotary_dim: int, cu: torch.Tensor,
+                   len_before: torch.Tensor, sequences: int, n_tokens: int, out: torch.Tensor) -> None:
+    """The queries of the expanded form: the partial sums ``q`` ``[slices, tokens, heads * (dim + rot)]`` summed, every head's
+    last ``rot`` numbers rotated by the position (the first ``rotary_dim`` of them, halves paired), narrowed to ``out``."""
+    _need(inv_freq, torch.float32, "inverse frequencies")
+    p, splits, stride, cols = _projection(q)
+    if cols != heads * (dim + rot) or tuple(out.shape) != (n_tokens, cols) or not out.is_contiguous():
+        raise KernelError("latent_queries: shapes do not fit the sizes")
+    fn = _fn("latent_attention", "tt_latent_queries", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                       c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(p, splits, stride, heads, dim, rot, _ptr(inv_freq), rotary_dim, _ptr(cu), _ptr(len_before), sequences, n_tokens, _ptr(out),
+              dtype_code(out.dtype), _stream()), "latent_queries")
 
 
 # ------------------------------------------------------------------------------ routing
@@ -756,6 +810,39 @@ def route_topk(logits: torch.Tensor, top: int, groups: int, keep: int, gates: to
     fn = _fn("routing", "tt_route_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p])
     _check(fn(p, splits, stride, tokens, experts, top, groups, keep, _ptr(gates), _ptr(chosen), _ptr(weights), _stream()), "route_topk")
+
+
+def route_rows(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: int, gates: torch.Tensor, chosen: torch.Tensor,
+               weights: torch.Tensor) -> None:
+    """:func:`route_topk` with the router's product ``x @ w.T`` (float32 sums) in front, in one kernel: ``x`` ``[tokens,
+    hidden]`` and ``w`` ``[experts, hidden]``, each float32 or bfloat16."""
+    tokens, hidden = x.shape
+    experts = w.shape[0]
+    _need(gates, torch.float32, "gates")
+    _need(weights, torch.float32, "routing weights")
+    _need(chosen, torch.int32, "chosen experts")
+    if not x.is_contiguous() or not w.is_contiguous() or w.shape[1] != hidden:
+        raise KernelError("route_rows: the rows and the router's matrix must be contiguous and of one width")
+    if not route_rows_takes(hidden, experts):
+        raise KernelError(f"route_rows stages a row of up to {ROUTE_MAX_HIDDEN} numbers, got {hidden}")
+    if (experts > ROUTE_MAX_EXPERTS or not 1 <= top <= min(32, experts) or not 1 <= groups <= 32 or experts % groups
+            or not 1 <= keep <= groups):
+        raise KernelError(f"route_rows takes up to {ROUTE_MAX_EXPERTS} experts in up to 32 equal groups and up to 32 choices; got "
+                          f"{experts} experts, {groups} groups of which {keep} stay, top {top}")
+    if tuple(gates.shape) != (tokens, experts) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
+        raise KernelError("route_rows: outputs do not fit the sizes")
+    fn = _fn("routing", "tt_route_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(w), dtype_code(w.dtype), hidden, tokens, experts, top, groups, keep, _ptr(gates),
+              _ptr(chosen), _ptr(weights), _stream()), "route_rows")
+
+
+ROUTE_MAX_HIDDEN = 11000
+
+
+def route_rows_takes(hidden: int, experts: int) -> bool:
+    """Whether a token's row and its logits fit the shared memory :func:`route_rows` stages them in."""
+    return (hidden + experts + 32) * 4 <= 48 * 1024 and hidden <= ROUTE_MAX_HIDDEN
 
 
 def scale_expert_columns(act: torch.Tensor, width: int, gates: torch.Tensor) -> None:

@@ -7,9 +7,14 @@ rest are one rotated key part that all heads share.  Per head ``k = [W_uk c | k_
 score is ``(q . k) * scale`` over the last ``window`` positions (or all of them), softmax, then ``W_o`` on the
 concatenated heads.
 
-Only ``[c | k_rot]`` is cached: one row per token, one key/value head, no value pool.  Neither keys nor values
-are ever formed: the kernel folds ``W_uk`` into the query (``a = W_uk_h^T q_h``, so that ``q_h . W_uk_h c = a . c``)
-and applies ``W_uv_h`` once to the softmax-weighted sum of latents.  Norms, positions, angles, scores and softmax
+Only ``[c | k_rot]`` is cached: one row per token, one key/value head, no value pool.  Decoding (and every step
+the tensor-core kernels do not take) never forms keys or values: the kernel folds ``W_uk`` into the query
+(``a = W_uk_h^T q_h``, so that ``q_h . W_uk_h c = a . c``) and applies ``W_uv_h`` once to the softmax-weighted sum of
+latents.  Prompts in bfloat16 whose heads have a size the tcgen05 attention kernel takes (``dim + rot_dim ==
+value_dim`` of 64 or 128) expand the latents the step can see into per-head keys and values for the length of the
+step, in scratch memory laid out like blocks of the ordinary cache, with one product over ``[W_uk; W_uv]``, and run
+that kernel on them: a prompt's arithmetic is then that of ordinary heads (``dim + rot_dim + value_dim`` numbers a
+pair instead of ``2 kv_rank + rot_dim``) and runs on the tensor cores.  Norms, positions, angles, scores and softmax
 weights are float32 in both dtypes.
 """
 from __future__ import annotations
@@ -85,9 +90,10 @@ class LatentAttention(Mixer):
         self.q_norm = tensors[n["dq_norm"]].to(torch.float32).contiguous()
         self.kv_norm = tensors[n["dkv_norm"]].to(torch.float32).contiguous()
         self.w_key, self.w_value = tensors[n["uk"]].contiguous(), tensors[n["uv"]].contiguous()
+        self.expander = Linear(torch.cat([self.w_key, self.w_value], dim=0))        # [W_uk; W_uv]: a latent into all heads' keys and values
 
     def projections(self) -> list:
-        return [self.down, self.up_q, Linear(self.w_key), Linear(self.w_value), self.out]
+        return [self.down, self.up_q, self.expander, self.out]
 
     def vectors(self) -> list[torch.Tensor]:
         return [self.q_norm, self.kv_norm]
@@ -107,16 +113,51 @@ class LatentAttention(Mixer):
                            ctx.sequences, ctx.n_tokens, ctx.status)
         q = self.up_q(ctx, q_latent, "latent.up_q")
         mixed = ctx.scratch("latent.mixed", (ctx.n_tokens, self.heads * self.value_dim))
+        if self.expands(ctx, x):
+            self.attend_expanded(ctx, q, cache, table, mixed)
+            return self.out.delta(ctx, mixed, "latent.out")
         splits = 1
         if ctx.decode:
             # keys of a decode step are cut into slices until the (token, head) warps fill the GPU; a window bounds the keys
             reach = ctx.max_total if self.window is None else min(self.window, ctx.max_total)
-            splits = min(kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(ctx.status.device)), max(1, reach // 256))
-        part_acc = part_ml = None
-        if splits > 1:
-            part_acc = ctx.scratch("latent.part_acc", (ctx.n_tokens * self.heads * splits * self.kv_rank,), torch.float32)
-            part_ml = ctx.scratch("latent.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
+            splits = min(kv_splits(ctx, ctx.n_tokens * self.heads, 64, 16 * api.sm_count(ctx.status.device)), max(1, reach // 64))
+        absorbed = ctx.scratch("latent.absorbed", (ctx.n_tokens * self.heads * (self.kv_rank + self.rot_dim),), torch.float32)
+        part_acc = ctx.scratch("latent.part_acc", (ctx.n_tokens * self.heads * splits * self.kv_rank,), torch.float32)
+        part_ml = ctx.scratch("latent.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
         api.latent_attention(q, self.w_key, self.w_value, cache.k_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                              self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, rot.inv_freq, rot.rotary_dim, self.scale,
-                             self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+                             self.window or 0, splits, mixed, absorbed, part_acc, part_ml, ctx.status)
         return self.out.delta(ctx, mixed, "latent.out")
+
+    # ------------------------------------------------------------ prompts on the tensor cores
+    EXPAND_FROM = 128           # packed tokens from which a step of prompts is expanded
+
+    def expands(self, ctx, x) -> bool:
+        head = self.dim + self.rot_dim
+        return (not ctx.decode and ctx.n_tokens >= self.EXPAND_FROM and x.dtype == torch.bfloat16 and head == self.value_dim
+                and self.w_key.dtype == torch.bfloat16 and api.attention_tcgen05_supports(x.dtype, self.heads, self.heads, head))
+
+    def expansion_bound(self, ctx, width: int) -> int:
+        """Temporary blocks the step can need, from the step's shape alone (a replayed step has other lengths): every
+        sequence sees its new tokens and at most ``window - 1`` before them, in blocks of 64 that may be cut at both ends."""
+        if self.window is None:
+            return ctx.sequences * width
+        return min(ctx.sequences * width, (ctx.n_tokens + ctx.sequences * (self.window - 1)) // 64 + 2 * ctx.sequences)
+
+    def attend_expanded(self, ctx, q, cache, table, mixed) -> None:
+        head = self.dim + self.rot_dim
+        blocks = self.expansion_bound(ctx, table.shape[1])
+        plan = ctx.scratch("latent.plan", (2 * ctx.sequences + 1,), torch.int32)
+        table_tmp = ctx.scratch("latent.table", tuple(table.shape), torch.int32)
+        latents = ctx.scratch("latent.visible", (blocks * 64, self.kv_rank))
+        keys = ctx.scratch("latent.keys", (blocks, self.heads, 64, head))
+        values = ctx.scratch("latent.values", (blocks, self.heads, self.value_dim, 64))
+        api.latent_expand(cache.k_pool, table, ctx.cu, ctx.len_before, ctx.sequences, self.window or 0, blocks, self.heads, self.dim,
+                          self.rot_dim, self.kv_rank, plan, table_tmp, latents, keys, ctx.status)
+        expanded = self.expander(ctx, latents, "latent.expand")
+        api.latent_scatter(expanded, self.heads, self.dim, self.rot_dim, self.value_dim, keys, values)
+        queries = ctx.scratch("latent.queries", (ctx.n_tokens, self.heads * head))
+        api.latent_queries(q, self.heads, self.dim, self.rot_dim, self.rot.inv_freq, self.rot.rotary_dim, ctx.cu, ctx.len_before,
+                           ctx.sequences, ctx.n_tokens, queries)
+        api.attention_tcgen05(queries, keys, values, table_tmp, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.heads,
+                              head, self.scale, self.window or 0, mixed, ctx.status)

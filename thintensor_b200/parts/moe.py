@@ -70,8 +70,8 @@ class MixtureOfExperts(FeedForward):
         self.gate_up = GatedLinear(torch.cat([tensors[g] for g, _, _ in names], dim=0), torch.cat([tensors[u] for _, u, _ in names], dim=0),
                                    None, None, self.activation)
         self.down = Linear(torch.cat([tensors[d] for _, _, d in names], dim=1))
-        # the router runs the exact float32 product in both dtypes
-        self.router = Linear(tensors[self.names["router"]].to(torch.float32))
+        # the router's sums are float32 in both dtypes; its matrix stays as stored (widening bfloat16 changes nothing)
+        self.router = Linear(tensors[self.names["router"]])
 
     def projections(self) -> list:
         return [self.router, self.gate_up.fused, self.down]
@@ -81,11 +81,15 @@ class MixtureOfExperts(FeedForward):
 
     def forward(self, ctx, x) -> Delta:
         tokens = ctx.n_tokens
-        logits = self.router(ctx, x, "moe.router")
         gates = ctx.scratch("moe.gates", (tokens, self.experts), torch.float32)
         chosen = ctx.scratch("moe.chosen", (tokens, self.top), torch.int32)
         weights = ctx.scratch("moe.weights", (tokens, self.top), torch.float32)
-        api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights)
+        if api.route_rows_takes(self.hidden, self.experts):
+            api.route_rows(x, self.router.weight, self.top, self.groups, self.keep, gates, chosen, weights)
+        else:                                   # rows too wide to stage: the exact product, then the routing
+            logits = ctx.scratch("moe.router", (1, tokens, self.experts), torch.float32)
+            api.gemm_simt(x, self.router.weight, None, logits)
+            api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights)
         act = self.gate_up(ctx, x, "moe.gate_up")
         api.scale_expert_columns(act, self.inter, gates)
         return self.down.delta(ctx, act, "moe.down")
