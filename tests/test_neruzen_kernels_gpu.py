@@ -72,7 +72,8 @@ def latent_plain(q, w_key, w_value, cached, pos, heads, dim, rot, vdim, rank, in
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,rot,vdim,rank,window", [(3, 16, 8, 24, 32, 0), (2, 40, 16, 8, 72, 37), (5, 8, 32, 48, 16, 64), (1, 24, 8, 40, 136, 1)])
+@pytest.mark.parametrize("heads,dim,rot,vdim,rank,window", [(3, 16, 8, 24, 32, 0), (2, 40, 16, 8, 72, 37), (5, 8, 32, 48, 16, 64), (1, 24, 8, 40, 136, 1),
+                                                            (2, 12, 6, 10, 18, 5), (3, 20, 4, 12, 20, 0)])
 def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window):
     """Sequences of unequal lengths, prompts (several new tokens) and decoding (one), through a scrambled table.  In every
     sequence one key far back is made to dominate a head's scores; with a window, that key stands just inside the window of
@@ -81,7 +82,7 @@ def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window
 
     g = torch.Generator().manual_seed(heads * 100 + rank)
     row = rank + rot
-    rotary_dim = rot if rank % 3 else rot // 2
+    rotary_dim = rot if rank % 3 else rot // 4 * 2
     inv_freq = (10000.0 ** (-torch.arange(0, max(rotary_dim, 2), 2, dtype=torch.float64) / max(rotary_dim, 2))).float().to(DEV)
     scale = 0.2
     totals, new = [300, 410, 70, 131], [5, 1, 70, 1]

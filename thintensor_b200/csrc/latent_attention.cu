@@ -136,15 +136,47 @@ __global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, 
     }
     for (int r = threadIdx.x; r < rank; r += blockDim.x) {
         const TW* col = w_key + (size_t)h * dim * rank + r;
-        float a0 = 0.0f, a1 = 0.0f;
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = 0.0f;
         int d = 0;
-        for (; d + 2 <= dim; d += 2) {
-            a0 = fmaf(lat_weight(col + (size_t)d * rank), lat_shared[d], a0);
-            a1 = fmaf(lat_weight(col + (size_t)(d + 1) * rank), lat_shared[d + 1], a1);
+        for (; d + 8 <= dim; d += 8) {                          // eight loads in flight, eight sums that do not wait for each other
+            float w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = lat_weight(col + (size_t)(d + i) * rank);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = fmaf(w[i], lat_shared[d + i], a[i]);
         }
-        if (d < dim) a0 = fmaf(lat_weight(col + (size_t)d * rank), lat_shared[d], a0);
-        out[r] = (a0 + a1) * scale;
+        for (; d < dim; ++d) a[0] = fmaf(lat_weight(col + (size_t)d * rank), lat_shared[d], a[0]);
+        out[r] = (((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]))) * scale;
     }
+}
+
+// a cache row times the folded query: 16 bytes a load, four loads asked for before their products
+template <typename TC>
+__device__ __forceinline__ float lat_dot(const TC* __restrict__ row, const float* __restrict__ q, int n) {
+    constexpr int VEC = LatVec<TC>::N;
+    if (n % VEC) return dot16<TC>(row, q, n);
+    float s0 = 0.0f, s1 = 0.0f;
+    int d = 0;
+    for (; d + 4 * VEC <= n; d += 4 * VEC) {
+        float v[4][VEC];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) LatVec<TC>::load(row + d + i * VEC, v[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                if (i & 1) s1 = fmaf(v[i][e], q[d + i * VEC + e], s1); else s0 = fmaf(v[i][e], q[d + i * VEC + e], s0);
+            }
+    }
+    for (; d < n; d += VEC) {
+        float v[VEC];
+        LatVec<TC>::load(row + d, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s0 = fmaf(v[e], q[d + e], s0);
+    }
+    return s0 + s1;
 }
 
 // One warp per (token, head) and key slice.  window <= 0: all keys 0..pos.  window > 0: keys pos - window + 1 .. pos.
@@ -193,7 +225,7 @@ __global__ void latent_attention_kernel(const float* __restrict__ absorbed, cons
         float score = -INFINITY;
         if (key < end) {
             off = tt_cache_offset(table_row, key, 0, 1, row_len, pool_blocks, status);
-            if (off >= 0) score = dot16<TC>(pool + off, qa, row_len);
+            if (off >= 0) score = lat_dot<TC>(pool + off, qa, row_len);
         }
         const float m_tile = tt_warp_max(score);
         if (m_tile == -INFINITY) continue;
@@ -248,6 +280,120 @@ __global__ void latent_attention_kernel(const float* __restrict__ absorbed, cons
     }
 }
 
+// The same for rows of whole 16-byte pieces (rank and rank + rot multiples of LatVec<TC>::N): the lanes of a warp lie ACROSS
+// a cache row, lane l holding pieces l, l + 32, ... of it, so a key is three or four loads of 512 contiguous bytes for the
+// warp (a lane per key read 32 different lines with every load), and the pieces that make the score are the pieces that
+// are accumulated as the value.  Four keys are taken together: their loads are in flight at once, their scores are summed
+// over the lanes side by side, and the running maximum moves once for the four.
+template <typename TC>
+__global__ void latent_attention_rows_kernel(const float* __restrict__ absorbed, const TC* __restrict__ pool,
+                                             const int* __restrict__ table, int table_width, int pool_blocks,
+                                             const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
+                                             int n_tokens, int heads, int rot, int rank, int window, int splits,
+                                             float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    constexpr int VEC = LatVec<TC>::N, ROW_PIECES = LAT_MAX_ROW / VEC / 32, VAL_PIECES = LAT_MAX_RANK / VEC / 32, KEYS = 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * LAT_WARPS + warp;   // (token, head)
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads);
+    const int split = blockIdx.y;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    const int* table_row = table + (size_t)b * table_width;
+    const int row_len = rank + rot;
+    float qa[ROW_PIECES][VEC];                                  // this lane's pieces of the folded query
+    const float* src = absorbed + (size_t)item * row_len;
+#pragma unroll
+    for (int c = 0; c < ROW_PIECES; ++c) {
+        const int r = (lane + 32 * c) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qa[c][e] = r < row_len ? src[r + e] : 0.0f;
+    }
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_keys = pos - first + 1;
+    int per = (n_keys + splits - 1) / splits;
+    per = (per + 31) & ~31;
+    const int begin = first + split * per;
+    const int end = min(begin + per, pos + 1);
+
+    float acc[VAL_PIECES][VEC];
+#pragma unroll
+    for (int c = 0; c < VAL_PIECES; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[c][e] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    for (int base = begin; base < end; base += KEYS) {
+        float v[KEYS][VAL_PIECES][VEC];                         // the latent pieces stay for the value sum
+        float score[KEYS];
+        bool live[KEYS];
+#pragma unroll
+        for (int k = 0; k < KEYS; ++k) {
+            const int key = base + k;
+            long long off = -1;
+            if (key < end) off = tt_cache_offset(table_row, key, 0, 1, row_len, pool_blocks, status);
+            live[k] = off >= 0;
+            float s = 0.0f;
+#pragma unroll
+            for (int c = 0; c < ROW_PIECES; ++c) {
+                const int r = (lane + 32 * c) * VEC;
+                float piece[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) piece[e] = 0.0f;
+                if (live[k] && r < row_len) LatVec<TC>::load(pool + off + r, piece);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) s = fmaf(piece[e], qa[c][e], s);
+                if (c < VAL_PIECES) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) v[k][c][e] = r < rank ? piece[e] : 0.0f;
+                }
+            }
+            score[k] = s;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < KEYS; ++k) score[k] += __shfl_xor_sync(0xffffffffu, score[k], o);
+        float m_new = m_run;
+#pragma unroll
+        for (int k = 0; k < KEYS; ++k)
+            if (live[k]) m_new = fmaxf(m_new, score[k]);
+        if (m_new == -INFINITY) continue;
+        const float corr = expf(m_run - m_new);                 // 0 before the first key
+        float p[KEYS];
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < KEYS; ++k) {
+            p[k] = live[k] ? expf(score[k] - m_new) : 0.0f;
+            sum += p[k];
+        }
+        l_run = l_run * corr + sum;
+        m_run = m_new;
+#pragma unroll
+        for (int c = 0; c < VAL_PIECES; ++c)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float a = acc[c][e] * corr;
+#pragma unroll
+                for (int k = 0; k < KEYS; ++k) a = fmaf(p[k], v[k][c][e], a);
+                acc[c][e] = a;
+            }
+    }
+    const size_t slot = (size_t)item * splits + split;
+#pragma unroll
+    for (int c = 0; c < VAL_PIECES; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const int r = (lane + 32 * c) * VEC + e;
+            if (r < rank) part_acc[slot * rank + r] = acc[c][e];
+        }
+    if (lane == 0) {
+        part_ml[slot * 2] = m_run;
+        part_ml[slot * 2 + 1] = l_run;
+    }
+}
+
 // One block per (token, head): combines the key slices in slice order into the normalised sum of latents, then a warp per
 // output number takes Wv_h's row times it, lanes across the latent.
 template <typename TOut, typename TW>
@@ -255,7 +401,7 @@ __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, c
                                            int vdim, int heads, const TW* __restrict__ w_value, TOut* __restrict__ out) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float lat_shared[];                       // rank
+    extern __shared__ float lat_shared[];                       // rank, then splits
     const size_t row = blockIdx.x;
     const int h = (int)(row % heads);
     const float* ml = part_ml + row * splits * 2;
@@ -265,16 +411,40 @@ __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, c
     for (int s = 0; s < splits; ++s)
         if (ml[2 * s] != -INFINITY) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    float* weight = lat_shared + rank;                          // a slice's share: exp(m_s - m) / l
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) weight[s] = ml[2 * s] != -INFINITY ? expf(ml[2 * s] - m) * inv : 0.0f;
+    __syncthreads();
     for (int r = threadIdx.x; r < rank; r += blockDim.x) {
         float acc = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = ml[2 * s];
-            if (ms != -INFINITY) acc = fmaf(part_acc[(row * splits + s) * rank + r], expf(ms - m), acc);
-        }
-        lat_shared[r] = acc * inv;
+        for (int s = 0; s < splits; ++s) acc = fmaf(part_acc[(row * splits + s) * rank + r], weight[s], acc);
+        lat_shared[r] = acc;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    constexpr int VEC = LatVec<TW>::N;
+    if (rank % VEC == 0) {                                      // 16 bytes of a row a load; four rows' loads in flight together
+        for (int v0 = 4 * warp; v0 < vdim; v0 += 4 * warps) {
+            float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int r = lane * VEC; r < rank; r += 32 * VEC) {
+                float w[4][VEC];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (v0 + i < vdim) LatVec<TW>::load(w_value + ((size_t)h * vdim + v0 + i) * rank + r, w[i]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (v0 + i < vdim) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) o[i] = fmaf(w[i][e], lat_shared[r + e], o[i]);
+                    }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float total = tt_warp_sum(o[i]);
+                if (lane == 0 && v0 + i < vdim) out[row * vdim + v0 + i] = tt_from_float<TOut>(total);
+            }
+        }
+        return;
+    }
     for (int v = warp; v < vdim; v += warps) {
         const TW* wrow = w_value + ((size_t)h * vdim + v) * rank;
         float o = 0.0f;
@@ -316,11 +486,18 @@ extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_str
     if (rows > 2147483647LL) return (int)cudaErrorInvalidValue;
     const size_t shared = (size_t)LAT_WARPS * (rank + rot) * sizeof(float);
     const dim3 grid((unsigned)blocks, splits), block(LAT_WARPS * 32);
-#define TT_ABSORB(TW) tt_launch_pdl(latent_absorb_kernel<TW>, dim3((unsigned)rows), dim3(128), (size_t)(dim + rot) * sizeof(float), stream, q, q_splits, (size_t)q_stride, (const TW*)w_key, cu, len_before, sequences, heads, dim, rot, rank, inv_freq, rotary_dim, scale, absorbed)
+#define TT_ABSORB(TW) tt_launch_pdl(latent_absorb_kernel<TW>, dim3((unsigned)rows), dim3(rank >= 512 ? 512 : rank >= 256 ? 256 : 128), (size_t)(dim + rot) * sizeof(float), stream, q, q_splits, (size_t)q_stride, (const TW*)w_key, cu, len_before, sequences, heads, dim, rot, rank, inv_freq, rotary_dim, scale, absorbed)
 #define TT_ATT(TA) tt_launch_pdl(latent_attention_kernel<TA>, grid, block, shared, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
-#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_expand_kernel<TA, TW>, dim3((unsigned)rows), dim3(128), (size_t)rank * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, (const TW*)w_value, (TA*)out)
+#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_expand_kernel<TA, TW>, dim3((unsigned)rows), dim3(256), (size_t)(rank + splits) * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, (const TW*)w_value, (TA*)out)
     if (weight_dtype == TT_F32) TT_ABSORB(float); else TT_ABSORB(__nv_bfloat16);
-    if (act_dtype == TT_F32) TT_ATT(float); else TT_ATT(__nv_bfloat16);
+#define TT_ATT_ROWS(TA) tt_launch_pdl(latent_attention_rows_kernel<TA>, grid, block, 0, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
+    const int piece = act_dtype == TT_F32 ? 4 : 8;              // numbers in 16 bytes of a cache row
+    if (rank % piece == 0 && rot % piece == 0) {
+        if (act_dtype == TT_F32) TT_ATT_ROWS(float); else TT_ATT_ROWS(__nv_bfloat16);
+    } else {
+        if (act_dtype == TT_F32) TT_ATT(float); else TT_ATT(__nv_bfloat16);
+    }
+#undef TT_ATT_ROWS
     if (act_dtype == TT_F32 && weight_dtype == TT_F32) TT_MERGE(float, float);
     else if (act_dtype == TT_F32) TT_MERGE(float, __nv_bfloat16);
     else if (weight_dtype == TT_F32) TT_MERGE(__nv_bfloat16, float);

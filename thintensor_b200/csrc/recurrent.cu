@@ -482,7 +482,8 @@ extern "C" int tt_linear_attention_prepare(const float* proj, int splits, long l
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || 2 * heads * D + heads * V > cols) return (int)cudaErrorInvalidValue;
     const int total = 2 * heads * D + heads * V;
-    const int tiles = n_tokens >= 1024 ? 1 : (total + 255) / 256 < 32 ? (total + 255) / 256 : 32;     // few tokens: a token's columns over several blocks
+    const int want = n_tokens >= 1024 ? (total + 1023) / 1024 : (total + 255) / 256;                // few tokens: a token's columns over more blocks
+    const int tiles = want < 32 ? want : 32;
     tt_launch_pdl(linear_attention_prepare_kernel, dim3(n_tokens, tiles), dim3(256), 0, stream, proj, splits, (size_t)split_stride, cols, heads, D,
                   V, activation, inv_freq, rotary_dim, k_scale, vkq, cu, len_before, sequences);
     TT_LAUNCH_CHECK();

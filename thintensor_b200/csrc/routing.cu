@@ -143,14 +143,17 @@ __global__ void route_rows_kernel(const TX* __restrict__ x, const TW* __restrict
     __syncthreads();
     for (int e = warp; e < experts; e += warps) {
         const TW* row = w + (size_t)e * hidden;
-        float a0 = 0.0f, a1 = 0.0f;
+        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         int j = lane;
-        for (; j + 32 < hidden; j += 64) {
-            a0 = fmaf(tt_to_float(row[j]), route_shared[j], a0);
-            a1 = fmaf(tt_to_float(row[j + 32]), route_shared[j + 32], a1);
+        for (; j + 96 < hidden; j += 128) {                     // four loads in flight, four sums
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = tt_to_float(row[j + 32 * i]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = fmaf(v[i], route_shared[j + 32 * i], a[i]);
         }
-        if (j < hidden) a0 = fmaf(tt_to_float(row[j]), route_shared[j], a0);
-        const float z = tt_warp_sum(a0 + a1);
+        for (; j < hidden; j += 32) a[0] = fmaf(tt_to_float(row[j]), route_shared[j], a[0]);
+        const float z = tt_warp_sum((a[0] + a[1]) + (a[2] + a[3]));
         if (lane == 0) logits[e] = z;
     }
     __syncthreads();
@@ -211,7 +214,7 @@ extern "C" int tt_route_rows(const void* x, int x_dtype, const void* w, int w_dt
         return (int)cudaErrorInvalidValue;
     const size_t shared = (size_t)(hidden + experts + 32) * sizeof(float);
     if (shared > 48 * 1024) return (int)cudaErrorInvalidValue;
-#define TT_ROUTE(TX, TW) tt_launch_pdl(route_rows_kernel<TX, TW>, dim3(n_tokens), dim3(128), shared, stream, (const TX*)x, (const TW*)w, hidden, n_tokens, experts, top, groups, keep, gates, chosen, weights)
+#define TT_ROUTE(TX, TW) tt_launch_pdl(route_rows_kernel<TX, TW>, dim3(n_tokens), dim3(n_tokens <= 256 ? 512 : 128), shared, stream, (const TX*)x, (const TW*)w, hidden, n_tokens, experts, top, groups, keep, gates, chosen, weights)
     if (x_dtype == TT_F32 && w_dtype == TT_F32) TT_ROUTE(float, float);
     else if (x_dtype == TT_F32) TT_ROUTE(float, __nv_bfloat16);
     else if (w_dtype == TT_F32) TT_ROUTE(__nv_bfloat16, float);
