@@ -73,7 +73,7 @@ def latent_plain(q, w_key, w_value, cached, pos, heads, dim, rot, vdim, rank, in
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,dim,rot,vdim,rank,window", [(3, 16, 8, 24, 32, 0), (2, 40, 16, 8, 72, 37), (5, 8, 32, 48, 16, 64), (1, 24, 8, 40, 136, 1),
-                                                            (2, 12, 6, 10, 18, 5), (3, 20, 4, 12, 20, 0)])
+                                                            (2, 12, 6, 10, 18, 5), (3, 20, 4, 12, 20, 0), (4, 32, 16, 24, 64, 200), (18, 8, 16, 8, 48, 0)])
 def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window):
     """Sequences of unequal lengths, prompts (several new tokens) and decoding (one), through a scrambled table.  In every
     sequence one key far back is made to dominate a head's scores; with a window, that key stands just inside the window of
@@ -120,8 +120,13 @@ def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window
     moved = latent_plain(queries[0][-1].float().double(), w_key, w_value, shadow, totals[0] - 1, heads, dim, rot, vdim, rank, inv_freq,
                          rotary_dim, scale, window)
     assert float((moved - want[cu[1] - 1]).abs().max()) > 0.05
-    for splits in (1, 3):
-        if splits > 1:
+    mma = dtype == torch.bfloat16 and api.latent_decode_tensor_cores(dtype, rank, rot)
+    for splits in (1, 3) + ((-1,) if mma else ()):
+        tensor_cores = splits < 0                               # decoding with the heads as the rows of tensor-core products
+        if tensor_cores:
+            reach = max(totals) if window <= 0 else min(window, max(totals))
+            splits = -(-reach // api.LATENT_DECODE_SLICE)
+        if splits > 1 or tensor_cores:
             # slices are for steps of one token per sequence: run the two decoding sequences alone
             pick = [b for b in range(len(new)) if new[b] == 1]
         else:
@@ -137,11 +142,11 @@ def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window
         part_ml = torch.zeros(len(rows_of) * heads * splits * 2, dtype=torch.float32, device=DEV)
         word = status()
         api.latent_attention(q_step, w_key_d, w_value_d, pool, table[pick].contiguous(), i32(cu_step), i32([before[b] for b in pick]), len(pick),
-                             len(rows_of), heads, dim, rot, vdim, rank, inv_freq, rotary_dim, scale, window, splits, out, absorbed, part_acc, part_ml, word)
+                             len(rows_of), heads, dim, rot, vdim, rank, inv_freq, rotary_dim, scale, window, splits, out, absorbed, part_acc, part_ml, word, tensor_cores)
         assert int(word.item()) == 0
         err = (out.double().cpu() - want[rows_of]).abs().max()
         bound = (1e-5 if dtype == torch.float32 else 0.03) * max(1.0, float(want.abs().max()))
-        assert float(err) <= bound, f"splits {splits}: {float(err):.3e} against logits up to {float(want.abs().max()):.2f}"
+        assert float(err) <= bound, f"splits {splits}, tensor cores {tensor_cores}: {float(err):.3e} against logits up to {float(want.abs().max()):.2f}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -20,6 +20,8 @@
 // tt_latent_expand_plan (which blocks of which sequence the step can see, and where they go), tt_latent_gather (their
 // latents into one matrix for the product with [Wk; Wv], their shared rotated parts into every head's keys),
 // tt_latent_scatter (the product's rows into keys and transposed values) and tt_latent_queries (rotated queries).
+#include <mma.h>
+
 #include "attention_kernels.cuh"
 
 constexpr int LAT_WARPS = 4;
@@ -394,6 +396,106 @@ __global__ void latent_attention_rows_kernel(const float* __restrict__ absorbed,
     }
 }
 
+// Decoding on the tensor cores (bfloat16 caches whose rows are whole pieces of 16 numbers): one CTA per (sequence, slice
+// of LT_KEYS keys, group of 16 heads).  All heads of a token read the same cache rows, so the heads are the 16 rows of the
+// products: S [heads x keys] = A [heads x (rank + rot)] K^T with A the folded queries, then O [heads x rank] = P C with C
+// the latent part of the same rows.  The slice's rows and the folded queries are staged in shared memory once and serve
+// both products; the slice's maximum is known before the second product, so nothing is rescaled.  Every warp takes 16 of
+// the keys in the first product and every fourth 16-column piece of the latent in the second (warp-level
+// mma.sync through the wmma interface).  Slices are combined by latent_merge_expand_kernel.
+constexpr int LT_KEYS = 64, LT_HEADS = 16, LT_S_LD = LT_KEYS + 4, LT_P_LD = LT_KEYS + 8, LT_O_LD = 20;
+
+static size_t latent_decode_shared(int row_len) {
+    return (size_t)(LT_HEADS + LT_KEYS) * (row_len + 8) * sizeof(__nv_bfloat16) + (size_t)LT_HEADS * LT_S_LD * sizeof(float) +
+           (size_t)LT_HEADS * LT_P_LD * sizeof(__nv_bfloat16) + (size_t)4 * LT_HEADS * LT_O_LD * sizeof(float);
+}
+
+__global__ void __launch_bounds__(128)
+latent_decode_mma_kernel(const float* __restrict__ absorbed, const __nv_bfloat16* __restrict__ pool, const int* __restrict__ table,
+                         int table_width, int pool_blocks, const int* __restrict__ len_before, int heads, int rot, int rank,
+                         int window, int splits, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* status) {
+    using namespace nvcuda;
+    tt_pdl_launch_dependents();
+    extern __shared__ __align__(128) unsigned char lat_bytes[];
+    const int row_len = rank + rot, ld = row_len + 8;           // rows 16 bytes apart modulo 128: no bank is met twice
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lat_bytes);               // [16][ld]
+    __nv_bfloat16* k_s = q_s + LT_HEADS * ld;                                       // [64][ld]
+    float* s_s = reinterpret_cast<float*>(k_s + LT_KEYS * ld);                      // [16][LT_S_LD]
+    __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(s_s + LT_HEADS * LT_S_LD);  // [16][LT_P_LD]
+    float* o_s = reinterpret_cast<float*>(p_s + LT_HEADS * LT_P_LD);                // [4][16][LT_O_LD]
+    const int t = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * LT_HEADS;       // one token per sequence: token t is sequence t
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = len_before[t];
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int begin = first + split * LT_KEYS;
+    const int end = min(begin + LT_KEYS, pos + 1);
+    const int* table_row = table + (size_t)t * table_width;
+    const int pieces = row_len >> 3;                            // 16-byte pieces of a row
+    tt_pdl_wait();
+    for (int e = threadIdx.x; e < LT_KEYS * pieces; e += blockDim.x) {
+        const int r = e / pieces, c = e - r * pieces;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (begin + r < end) {
+            const long long off = tt_cache_offset(table_row, begin + r, 0, 1, row_len, pool_blocks, status);
+            if (off >= 0) v = *reinterpret_cast<const uint4*>(pool + off + 8 * c);
+        }
+        *reinterpret_cast<uint4*>(k_s + r * ld + 8 * c) = v;
+    }
+    for (int e = threadIdx.x; e < LT_HEADS * row_len; e += blockDim.x) {
+        const int r = e / row_len, c = e - r * row_len;
+        q_s[r * ld + c] = __float2bfloat16_rn(h0 + r < heads ? absorbed[((size_t)t * heads + h0 + r) * row_len + c] : 0.0f);
+    }
+    __syncthreads();
+    {   // S = A K^T: this warp's 16 keys
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.0f);
+        for (int k = 0; k < row_len; k += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
+            wmma::load_matrix_sync(a, q_s + k, ld);
+            wmma::load_matrix_sync(b, k_s + (16 * warp) * ld + k, ld);
+            wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(s_s + 16 * warp, acc, LT_S_LD, wmma::mem_row_major);
+    }
+    __syncthreads();
+    for (int r = 4 * warp; r < 4 * warp + 4; ++r) {            // softmax of a head's row over the slice, float32
+        const float s0 = begin + lane < end ? s_s[r * LT_S_LD + lane] : -INFINITY;
+        const float s1 = begin + lane + 32 < end ? s_s[r * LT_S_LD + lane + 32] : -INFINITY;
+        const float m = tt_warp_max(fmaxf(s0, s1));
+        const float p0 = s0 == -INFINITY ? 0.0f : expf(s0 - m), p1 = s1 == -INFINITY ? 0.0f : expf(s1 - m);
+        const float l = tt_warp_sum(p0 + p1);
+        p_s[r * LT_P_LD + lane] = __float2bfloat16_rn(p0);
+        p_s[r * LT_P_LD + lane + 32] = __float2bfloat16_rn(p1);
+        if (lane == 0 && h0 + r < heads) {
+            const size_t slot = ((size_t)t * heads + h0 + r) * splits + split;
+            part_ml[slot * 2] = m;
+            part_ml[slot * 2 + 1] = l;
+        }
+    }
+    __syncthreads();
+    float* mine = o_s + warp * LT_HEADS * LT_O_LD;
+    for (int f = warp; f < (rank >> 4); f += 4) {               // O = P C: 16 columns of the latent at a time
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.0f);
+#pragma unroll
+        for (int kk = 0; kk < LT_KEYS; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::row_major> b;
+            wmma::load_matrix_sync(a, p_s + kk, LT_P_LD);
+            wmma::load_matrix_sync(b, k_s + kk * ld + 16 * f, ld);
+            wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(mine, acc, LT_O_LD, wmma::mem_row_major);
+        __syncwarp();
+        for (int e = lane; e < LT_HEADS * 16; e += 32) {
+            const int r = e >> 4, c = e & 15;
+            if (h0 + r < heads) part_acc[(((size_t)t * heads + h0 + r) * splits + split) * rank + 16 * f + c] = mine[r * LT_O_LD + c];
+        }
+        __syncwarp();
+    }
+}
+
 // One block per (token, head): combines the key slices in slice order into the normalised sum of latents, then a warp per
 // output number takes Wv_h's row times it, lanes across the latent.
 template <typename TOut, typename TW>
@@ -476,7 +578,8 @@ extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_str
                                    int weight_dtype, const void* pool, int act_dtype, const int* table, int table_width, int pool_blocks,
                                    const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int dim, int rot,
                                    int vdim, int rank, const float* inv_freq, int rotary_dim, float scale, int window, int splits,
-                                   void* out, float* absorbed, float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+                                   void* out, float* absorbed, float* part_acc, float* part_ml, int one_token_each, unsigned* status,
+                                   cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rank > LAT_MAX_RANK || rank + rot > LAT_MAX_ROW || dim <= 0 || dim > LAT_MAX_DIM || vdim <= 0 || splits < 1 ||
         splits > 65535 || rotary_dim > rot || (rotary_dim & 1) || !absorbed || !part_acc || !part_ml)
@@ -492,7 +595,18 @@ extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_str
     if (weight_dtype == TT_F32) TT_ABSORB(float); else TT_ABSORB(__nv_bfloat16);
 #define TT_ATT_ROWS(TA) tt_launch_pdl(latent_attention_rows_kernel<TA>, grid, block, 0, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
     const int piece = act_dtype == TT_F32 ? 4 : 8;              // numbers in 16 bytes of a cache row
-    if (rank % piece == 0 && rot % piece == 0) {
+    if (one_token_each == 2) {                                  // the caller has checked tt_latent_decode_mma_takes and set splits for slices of LT_KEYS
+        static size_t allowed = 0;
+        const size_t need = latent_decode_shared(rank + rot);
+        if (need > allowed) {
+            const cudaError_t e = cudaFuncSetAttribute(latent_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+            if (e != cudaSuccess) return (int)e;
+            allowed = need;
+        }
+        tt_launch_pdl(latent_decode_mma_kernel, dim3(n_tokens, splits, (heads + LT_HEADS - 1) / LT_HEADS), dim3(128), need, stream,
+                      (const float*)absorbed, (const __nv_bfloat16*)pool, table, table_width, pool_blocks, len_before, heads, rot, rank, window,
+                      splits, part_acc, part_ml, status);
+    } else if (rank % piece == 0 && rot % piece == 0) {
         if (act_dtype == TT_F32) TT_ATT_ROWS(float); else TT_ATT_ROWS(__nv_bfloat16);
     } else {
         if (act_dtype == TT_F32) TT_ATT(float); else TT_ATT(__nv_bfloat16);
@@ -673,3 +787,10 @@ extern "C" int tt_latent_queries(const float* q, int splits, long long split_str
         tt_launch_pdl(latent_queries_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, heads, dim, rot, inv_freq, rotary_dim, cu, len_before, sequences, (__nv_bfloat16*)out);
     TT_LAUNCH_CHECK();
 }
+
+// Whether the tensor-core decode kernel takes these sizes (bfloat16 cache, latent and rotated part multiples of 16, shared memory), and
+// the keys of one of its slices.
+extern "C" int tt_latent_decode_mma_takes(int act_dtype, int rank, int rot) {
+    return act_dtype == TT_BF16 && rank % 16 == 0 && rot % 16 == 0 && rank + rot <= LAT_MAX_ROW && latent_decode_shared(rank + rot) <= 200 * 1024;
+}
+extern "C" int tt_latent_decode_slice_keys() { return LT_KEYS; }

@@ -698,7 +698,8 @@ def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int, q_weigh
 def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor, pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                      len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, dim: int, rot: int, vdim: int, rank: int,
                      inv_freq: torch.Tensor, rotary_dim: int, scale: float, window: int, splits: int, out: torch.Tensor,
-                     absorbed: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, status: torch.Tensor) -> None:
+                     absorbed: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, status: torch.Tensor,
+                     tensor_cores: bool = False) -> None:
     """Causal softmax attention over a latent cache.  ``q``: float32 partial sums ``[slices, tokens, heads * (dim + rot)]`` of
     the queries (per head ``dim`` unrotated numbers, then ``rot`` of which the first ``rotary_dim`` are rotated here);
     ``w_key`` ``[heads * dim, rank]`` and ``w_value`` ``[heads * vdim, rank]`` expand a latent into a head's keys and values;
@@ -706,7 +707,11 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
     query i and key j: ``(q_plain . w_key_h c_j + q_rot . k_rot_j) * scale`` for ``0 <= i - j < window`` (``window`` 0: every
     earlier key); ``out`` ``[tokens, heads * vdim]``.  Scratch memory, all float32: ``absorbed`` ``[tokens * heads * (rank +
     rot)]`` for the queries with ``w_key`` folded in; ``part_acc`` ``[tokens * heads * splits * rank]`` and ``part_ml``
-    ``[tokens * heads * splits * 2]`` for the ``splits`` slices the keys are cut into."""
+    ``[tokens * heads * splits * 2]`` for the ``splits`` slices the keys are cut into.  ``tensor_cores``: a step of one token per
+    sequence whose sizes :func:`latent_decode_tensor_cores` takes runs both products on the tensor cores, with the heads of a
+    token as the rows; ``splits`` must then cover every key a token can see in slices of ``LATENT_DECODE_SLICE`` keys."""
+    if tensor_cores and (n_tokens != sequences or not latent_decode_tensor_cores(out.dtype, rank, rot)):
+        raise KernelError("latent_attention: the tensor-core form is for steps of one token per sequence and sizes it takes")
     _need(inv_freq, torch.float32, "inverse frequencies")
     if rank > LATENT_MAX_RANK or rank + rot > LATENT_MAX_ROW or dim > LATENT_MAX_DIM:
         raise KernelError(f"latent attention takes latents of up to {LATENT_MAX_RANK}, rows of up to {LATENT_MAX_ROW} and "
@@ -725,11 +730,27 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
     fn = _fn("latent_attention", "tt_latent_attention", [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                                          c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                          c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                         c_void_p, c_void_p])
+                                                         c_int, c_void_p, c_void_p])
     _check(fn(p, q_splits, q_stride, _ptr(w_key), _ptr(w_value), dtype_code(w_key.dtype), _ptr(pool), dtype_code(out.dtype), _ptr(table),
               table.shape[1], pool.shape[0], _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, dim, rot, vdim, rank, _ptr(inv_freq),
-              rotary_dim, scale, window, splits, _ptr(out), _ptr(absorbed), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()),
-           "latent_attention", 3)
+              rotary_dim, scale, window, splits, _ptr(out), _ptr(absorbed), _ptr(part_acc), _ptr(part_ml), 2 if tensor_cores else 0, _ptr(status),
+              _stream()), "latent_attention", 3)
+
+
+LATENT_DECODE_SLICE = 64        # keys of one slice of the tensor-core decode form (LT_KEYS in csrc/latent_attention.cu)
+
+
+def latent_decode_tensor_cores(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """Whether :func:`latent_attention` can decode on the tensor cores: a bfloat16 cache whose latent and rotated part are
+    multiples of 16 numbers and whose staged slice fits the shared memory."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = _functions.get("tt_latent_decode_mma_takes")
+    if fn is None:
+        fn = getattr(build.load("latent_attention"), "tt_latent_decode_mma_takes")
+        fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
+        _functions["tt_latent_decode_mma_takes"] = fn
+    return bool(fn(BF16, rank, rot))
 
 
 def latent_expand(pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor, sequences: int, window: int,

@@ -116,17 +116,21 @@ class LatentAttention(Mixer):
         if self.expands(ctx, x):
             self.attend_expanded(ctx, q, cache, table, mixed)
             return self.out.delta(ctx, mixed, "latent.out")
-        splits = 1
-        if ctx.decode:
+        splits, tensor_cores = 1, False
+        reach = ctx.max_total if self.window is None else min(self.window, ctx.max_total)
+        if (ctx.decode and api.latent_decode_tensor_cores(mixed.dtype, self.kv_rank, self.rot_dim)
+                and -(-reach // api.LATENT_DECODE_SLICE) <= 256):
+            # decoding on the tensor cores: the heads of a token are the rows of both products, the keys go in slices of 64
+            splits, tensor_cores = -(-reach // api.LATENT_DECODE_SLICE), True
+        elif ctx.decode:
             # keys of a decode step are cut into slices until the (token, head) warps fill the GPU; a window bounds the keys
-            reach = ctx.max_total if self.window is None else min(self.window, ctx.max_total)
             splits = min(kv_splits(ctx, ctx.n_tokens * self.heads, 64, 16 * api.sm_count(ctx.status.device)), max(1, reach // 64))
         absorbed = ctx.scratch("latent.absorbed", (ctx.n_tokens * self.heads * (self.kv_rank + self.rot_dim),), torch.float32)
         part_acc = ctx.scratch("latent.part_acc", (ctx.n_tokens * self.heads * splits * self.kv_rank,), torch.float32)
         part_ml = ctx.scratch("latent.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
         api.latent_attention(q, self.w_key, self.w_value, cache.k_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                              self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, rot.inv_freq, rot.rotary_dim, self.scale,
-                             self.window or 0, splits, mixed, absorbed, part_acc, part_ml, ctx.status)
+                             self.window or 0, splits, mixed, absorbed, part_acc, part_ml, ctx.status, tensor_cores)
         return self.out.delta(ctx, mixed, "latent.out")
 
     # ------------------------------------------------------------ prompts on the tensor cores
