@@ -55,7 +55,7 @@ CONFIGS = {
                 "heads": 1, "dim": 48, "rot_dim": 8, "vdim": 16, "q_rank": 24, "kv_rank": 32, "scale": 0.3, "mask": {"size": 150},
                 "rot": {"dims": 8, "base": 100.0}}},
             {"type": "latent_attention", "mlp": _moe(4, 2, 32, (4, 2), 8), "mixer": {
-                "heads": 5, "dim": 8, "rot_dim": 24, "vdim": 12, "q_rank": 80, "kv_rank": 40, "scale": 0.125,
+                "heads": 5, "dim": 8, "rot_dim": 24, "vdim": 12, "q_rank": 80, "kv_rank": 40, "scale": 0.11,
                 "rot": {"dims": 24, "base": 1000000.0}}},
             {"type": "retention", "mlp": None, "mixer": {"heads": 3, "dim": 16, "vdim": 16, "decay": [0.8, 0.9, 0.99],
                                                          "rot": {"dims": 16, "base": 10000.0}}},
@@ -68,7 +68,7 @@ CONFIGS = {
         "embedding": {"bigram": {"buckets": 61, "mul_prev": 3, "mul_cur": 5}},
         "layers": [
             {"type": "latent_attention", "mlp": _moe(4, 2, 48, (2, 1), 64), "mixer": {
-                "heads": 2, "dim": 32, "rot_dim": 32, "vdim": 64, "q_rank": 40, "kv_rank": 48, "scale": 0.125, "mask": {"size": 100},
+                "heads": 2, "dim": 32, "rot_dim": 32, "vdim": 64, "q_rank": 40, "kv_rank": 48, "scale": 0.13, "mask": {"size": 100},
                 "rot": {"dims": 32, "base": 10000.0}}},
             {"type": "lightning", "mlp": None, "mixer": {"heads": 2, "dim": 32, "vdim": 32, "decay": [0.9, 0.99]}},
             {"type": "latent_attention", "mlp": None, "mixer": {

@@ -372,13 +372,13 @@ def random_config(seed: int) -> dict:
 
     def rotation(most):
         dims = r.choice([2, most // 2 // 2 * 2, most])
-        return {"dims": max(2, dims), "base": r.choice([100.0, 20000.0, 1e6])}
+        return {"dims": max(2, dims), "base": r.choice([100.0, 50000.0, 1e6])}
 
     def latent():
         rot_dim = r.choice([4, 8, 16, 40])
         mixer = {"heads": r.choice([1, 2, 4, 7]), "dim": r.choice([8, 20, 32, 72]), "rot_dim": rot_dim, "vdim": r.choice([6, 16, 34, 64]),
                  "q_rank": r.choice([12, 40, 96]), "kv_rank": r.choice([8, 24, 56, 136]), "scale": r.choice([0.1, 0.3, 0.05]),
-                 "rot": {"dims": rot_dim, "base": r.choice([100.0, 20000.0, 1e6])}}
+                 "rot": {"dims": rot_dim, "base": r.choice([100.0, 50000.0, 1e6])}}
         window = r.choice([None, 1, 2, 7, 33, 64, 65, 100])
         if window:
             mixer["mask"] = {"size": window}
@@ -411,7 +411,7 @@ def random_config(seed: int) -> dict:
     config = {"architecture": "Neruzen", "vocab": r.choice([50, 129, 300]), "width": r.choice([40, 90, 100, 128]),
               "norm": {"eps": r.choice([1e-6, 1e-5])}, "layers": layers}
     if r.random() < 0.8:
-        config["embedding"] = {"bigram": {"buckets": r.choice([1, 13, 257]), "mul_prev": r.choice([0, 1, 31, 1000003]), "mul_cur": r.choice([1, 17, 99991])}}
+        config["embedding"] = {"bigram": {"buckets": r.choice([1, 13, 257]), "mul_prev": r.choice([0, 1, 29, 1000003]), "mul_cur": r.choice([1, 19, 99991])}}
     return config
 
 
