@@ -432,19 +432,42 @@ latent_decode_mma_kernel(const float* __restrict__ absorbed, const __nv_bfloat16
     const int* table_row = table + (size_t)t * table_width;
     const int pieces = row_len >> 3;                            // 16-byte pieces of a row
     tt_pdl_wait();
+    // the slice's rows: asynchronous 16-byte copies, all of a thread's in flight together (one after the other they cost a
+    // round trip to the L2 each: 36 of them for a row of 576 numbers)
     for (int e = threadIdx.x; e < LT_KEYS * pieces; e += blockDim.x) {
         const int r = e / pieces, c = e - r * pieces;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (begin + r < end) {
-            const long long off = tt_cache_offset(table_row, begin + r, 0, 1, row_len, pool_blocks, status);
-            if (off >= 0) v = *reinterpret_cast<const uint4*>(pool + off + 8 * c);
+        long long off = -1;
+        if (begin + r < end) off = tt_cache_offset(table_row, begin + r, 0, 1, row_len, pool_blocks, status);
+        __nv_bfloat16* dst = k_s + r * ld + 8 * c;
+        if (off >= 0) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(pool + off + 8 * c) : "memory");
+        } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
-        *reinterpret_cast<uint4*>(k_s + r * ld + 8 * c) = v;
     }
-    for (int e = threadIdx.x; e < LT_HEADS * row_len; e += blockDim.x) {
-        const int r = e / row_len, c = e - r * row_len;
-        q_s[r * ld + c] = __float2bfloat16_rn(h0 + r < heads ? absorbed[((size_t)t * heads + h0 + r) * row_len + c] : 0.0f);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the folded queries: eight 16-byte loads asked for before the first is narrowed
+    const int quads = row_len >> 2;
+    for (int e0 = threadIdx.x; e0 < LT_HEADS * quads; e0 += 8 * blockDim.x) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = e0 + i * blockDim.x, r = e / quads, c = e - r * quads;
+            v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (e < LT_HEADS * quads && h0 + r < heads)
+                v[i] = *reinterpret_cast<const float4*>(absorbed + ((size_t)t * heads + h0 + r) * row_len + 4 * c);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = e0 + i * blockDim.x, r = e / quads, c = e - r * quads;
+            if (e < LT_HEADS * quads) {
+                __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(q_s + r * ld + 4 * c);
+                dst[0] = __floats2bfloat162_rn(v[i].x, v[i].y);
+                dst[1] = __floats2bfloat162_rn(v[i].z, v[i].w);
+            }
+        }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     {   // S = A K^T: this warp's 16 keys
         wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
@@ -518,6 +541,7 @@ __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, c
     __syncthreads();
     for (int r = threadIdx.x; r < rank; r += blockDim.x) {
         float acc = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) acc = fmaf(part_acc[(row * splits + s) * rank + r], weight[s], acc);
         lat_shared[r] = acc;
     }
