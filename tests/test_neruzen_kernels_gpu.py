@@ -76,8 +76,8 @@ def latent_plain(q, w_key, w_value, cached, pos, heads, dim, rot, vdim, rank, in
                                                             (2, 12, 6, 10, 18, 5), (3, 20, 4, 12, 20, 0), (4, 32, 16, 24, 64, 200), (18, 8, 16, 8, 48, 0)])
 def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window):
     """Sequences of unequal lengths, prompts (several new tokens) and decoding (one), through a scrambled table.  In every
-    sequence one key far back is made to dominate a head's scores; with a window, that key stands just inside the window of
-    the last token of the first sequence and just outside the window of the last token of the second."""
+    sequence one key is made to dominate a head's scores: without a window far back or at a cache block's border; with a
+    window just inside the last token's window for one prompt and one decoding sequence, just outside it for the other two."""
     from thintensor_b200.kernels import api
 
     g = torch.Generator().manual_seed(heads * 100 + rank)
@@ -96,8 +96,10 @@ def test_latent_attention_marked_keys(dtype, heads, dim, rot, vdim, rank, window
         rows = torch.randn(n, row, generator=g, dtype=torch.float64)
         q = torch.randn(new[b], heads * (dim + rot), generator=g, dtype=torch.float64)
         last = n - 1
-        marked = 3 if window <= 0 else (last - window + 1 if b % 2 == 0 else last - window)
-        marked = max(marked, 0)
+        # without a window: far back, at the last row of a cache block and the first of the next; with one: just inside the last
+        # token's window (the first prompt, the second decoding sequence) or just outside it (the others)
+        marked = [3, 63, 64, 127][b] if window <= 0 else (last - window + 1 if b in (0, 3) else last - window)
+        marked = min(max(marked, 0), last)
         a = w_key[:dim].T @ q[-1].reshape(heads, dim + rot)[0, :dim]                       # head 0 of the last query, folded
         rows[marked, :rank] = a / a.norm() * 25.0 / (scale * a.norm()) * a.norm()           # score of about 25 before the others' noise
         cached.append(fill_cache(pool, table, b, rows))
