@@ -1,6 +1,7 @@
-// Memory-bound kernels between the matrix products: embedding gather, residual add
-// fused with RMSNorm, rotary encoding fused with the cache append, SwiGLU, and the
-// length bookkeeping of a step.  All statistics, angles and sums are float32.
+// Memory-bound kernels between the matrix products: embedding gather (also with a hashed
+// row for the pair of the previous token and this one), residual add fused with RMSNorm,
+// the token shift of a mixer's input, rotary encoding fused with the cache append, SwiGLU,
+// and the length bookkeeping of a step.  All statistics, angles and sums are float32.
 //
 // Counterparts in random-unknown-username/Thintensor (Triton, one token per launch):
 // _copy_embed_token thinruntime/gpu_runtime.py:11396-11427; _rms_norm_kernel and

@@ -1,6 +1,7 @@
 // Kernels of the recurrent token mixers: the short causal convolution with its carried inputs, the
-// Mamba-2 state-space recurrence, the gated delta-rule recurrence, the gated group norm behind both,
-// and the weighted sum of two branches.  Everything here is float32: inputs are the float32 partial
+// Mamba-2 state-space recurrence (also run with a constant decay and step size one: the linear
+// attention S <- g S + k v^T, o = S^T q, whose q, k and v a kernel here prepares), the gated delta-rule
+// recurrence, the gated group norm behind them (gate: silu or sigmoid), and the weighted sum of two branches.  Everything here is float32: inputs are the float32 partial
 // sums of a projection ([splits][tokens][cols], summed on the way in), states live in float32 and are
 // carried per sequence slot, and only the normalised output that feeds the next matrix product is
 // narrowed to the activation dtype.
