@@ -123,6 +123,36 @@ def test_prompt_in_portions(folders, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
+def test_long_prompt_in_large_portions(folders, name, dtype):
+    """Portions of more than a hundred tokens far into a sequence: a window has by then given blocks back, and a portion's
+    first token looks back into blocks that earlier portions wrote (the expanded form of latent attention starts its
+    temporary blocks in the middle of the sequence)."""
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folders(name, dtype)
+    judge = Judge(dtype, folder)
+    engine = load(folder, dtype).new_engine(max_tokens=1024, max_sequences=2)
+    tokens = token_ids(CONFIGS[name]["vocab"], 420, 215)
+    other = token_ids(CONFIGS[name]["vocab"], 300, 216)
+    a, b = engine.open(), engine.open()
+    got, at = [], 0
+    for step, count in enumerate((150, 130, 140)):
+        rows = [0, count // 2, count - 2, count - 1]
+        entries = [Entry(a, tokens[at: at + count], rows)]
+        if step < 2:                                      # a second request beside it, in portions of another size
+            entries.append(Entry(b, other[150 * step: 150 * step + 150], [149]))
+        out = engine.step(entries)
+        got.append((at, rows, out))
+        at += count
+    engine.check_status()
+    for at, rows, out in got:
+        judge.add(out[: len(rows)], tokens, [at + r for r in rows], f"{name} portion at {at}")
+    judge.add(torch.stack([out[len(rows)] for _, rows, out in got[:2]]), other, [149, 299], f"{name} the request beside it")
+    judge.done()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
 def test_pieces_of_a_step(folders, name, dtype):
     """A step larger than the engine's limit runs in pieces; a sequence may straddle two of them."""
     from thintensor_b200.engine.engine import Entry
